@@ -1,0 +1,169 @@
+/*
+ * kvax_b200 — C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * Every entry point only enqueues work on the caller's stream.  The caller owns all
+ * buffers (inputs, outputs, workspace); nothing here allocates, frees, synchronises or
+ * throws.  Return value: 0 on success, a negative KVAX_B200_E* code for a rejected
+ * call.  Device-side protocol failures (a bounded wait that gave up) are reported
+ * through the optional int32 `status` word in device memory: 0 = ok.
+ *
+ * Each declaration cites the call site in the reference (nebius/kvax) whose
+ * `jt.triton_call(...)` custom call it replaces.
+ *
+ * Tensors use the public layout of the reference API: q/o/do/dq are (B, Sq, Hq, D),
+ * k/v/dk/dv are (B, Skv, Hkv, D), element strides given explicitly so that the
+ * (B, H, S, D) layout the reference uses internally can be passed as well.  The head
+ * dimension must be contiguous.
+ */
+#ifndef KVAX_B200_H_
+#define KVAX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* kvax_b200_stream_t; /* == cudaStream_t */
+
+enum {
+  KVAX_B200_OK = 0,
+  KVAX_B200_EINVAL = -1,      /* bad argument (null pointer, non-positive size, ...) */
+  KVAX_B200_EUNSUPPORTED = -2,/* shape or dtype outside what the kernels cover        */
+  KVAX_B200_EWORKSPACE = -3,  /* workspace too small or misaligned                    */
+  KVAX_B200_ELAUNCH = -4,     /* the CUDA runtime refused a launch or a tensor map    */
+  KVAX_B200_ENODEVICE = -5    /* no usable sm_100 device / driver entry point missing */
+};
+
+enum { KVAX_B200_BF16 = 0 };
+
+#define KVAX_B200_PADDING_SEGMENT_ID (-1) /* kvax/utils/common.py:9 */
+
+const char* kvax_b200_version(void);
+const char* kvax_b200_error_string(int code);
+
+/* ------------------------------------------------------------------------------------
+ * Block-mask builder.
+ * Replaces compute_attention_mask_kernel (kvax/ops/mask_creator.py:26-152) together with
+ * the host steps around its launch that belong to the bit-exact contract: padding to the
+ * block size (:212-225), the PAD -> kv_len_padded+1 remap (:247-259), and the
+ * "nothing found" fix-ups (:317-333).  One call builds up to three masks (forward, dq,
+ * dkdv — mask_creator.py:438-488) with two kernel launches in total.
+ * ---------------------------------------------------------------------------------- */
+typedef struct kvax_b200_mask_desc {
+  int32_t q_block;        /* query block size of this mask                               */
+  int32_t kv_block;       /* kv block size of this mask                                  */
+  int32_t kv_outer;       /* 0: one row per query block (forward / dq masks);
+                             1: one row per kv block (dkdv mask, calculate_dkdv_mask)    */
+  int32_t reserved;
+  int32_t* lower;         /* out, (B, n_outer) int32                                     */
+  int32_t* upper;         /* out                                                         */
+  int32_t* lower_full;    /* out                                                         */
+  int32_t* upper_full;    /* out                                                         */
+} kvax_b200_mask_desc;
+
+typedef struct kvax_b200_mask_params {
+  const int32_t* q_positions;    /* (B, Sq)  */
+  const int32_t* q_segment_ids;  /* (B, Sq)  */
+  const int32_t* kv_positions;   /* (B, Skv) */
+  const int32_t* kv_segment_ids; /* (B, Skv) */
+  int32_t batch, q_len, kv_len;
+  int32_t skip_pad_tokens;
+  int32_t n_masks;               /* 1..3 */
+  int32_t reserved;
+  kvax_b200_mask_desc masks[3];
+} kvax_b200_mask_params;
+
+size_t kvax_b200_mask_workspace_bytes(const kvax_b200_mask_params* p);
+int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
+                         kvax_b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Context-parallel token permutation (pure data movement, bit-exact).
+ * Replaces the XLA gather behind apply_permutation (kvax/utils/permutation.py:18-42):
+ * axis 1 of a (B, S, inner) array is cut into 2*cp chunks, chunk order becomes
+ * [0, 2cp-1, 1, 2cp-2, ...] (reverse = 0) or its inverse (reverse = 1).
+ * `row_bytes` is the size of one token (product of the trailing dims times the element
+ * size).
+ * ---------------------------------------------------------------------------------- */
+int kvax_b200_permute_tokens(const void* src, void* dst, int64_t batch, int64_t seq_len, int64_t row_bytes,
+                             int32_t cp, int32_t reverse, kvax_b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Flash attention, forward and backward.
+ * ---------------------------------------------------------------------------------- */
+typedef struct kvax_b200_block_mask {   /* one AttentionMask (kvax/utils/typing.py:15-37) */
+  const int32_t* lower;
+  const int32_t* upper;
+  const int32_t* lower_full;
+  const int32_t* upper_full;
+  int32_t q_block;   /* block sizes the mask was built with */
+  int32_t kv_block;
+} kvax_b200_block_mask;
+
+typedef struct kvax_b200_attn_shape {
+  int32_t batch, q_len, kv_len;
+  int32_t q_heads, kv_heads;
+  int32_t head_dim;        /* Dqk == Dv; 64 or 128                                       */
+  int32_t dtype;           /* KVAX_B200_BF16                                             */
+  int32_t assume_sequential_positions; /* causal test on indices + query_global_offset   */
+  float scale;
+  int32_t reserved;
+  /* element strides (batch, seq, head); head_dim stride is 1 */
+  int64_t q_strides[3], k_strides[3], v_strides[3], o_strides[3];
+  const int32_t* q_positions;    /* (B, Sq)  */
+  const int32_t* q_segment_ids;  /* (B, Sq)  */
+  const int32_t* kv_positions;   /* (B, Skv) */
+  const int32_t* kv_segment_ids; /* (B, Skv) */
+  /* Global index of local query token 0 / of the first token of the second half of the
+     local queries (context parallelism with the load-balancing permutation,
+     flash_attention_triton.py:1426-1447).  Both 0 without context parallelism; only read
+     when assume_sequential_positions != 0. */
+  int32_t q_global_offset_first, q_global_offset_second;
+} kvax_b200_attn_shape;
+
+/* Forward.  Replaces flash_attention_forward_kernel (flash_attention_triton.py:137-370,
+ * launched at :1517-1540): out (B, Sq, Hq, D) in the input dtype and the base-2
+ * log-sum-exp (B, Hq, Sq) fp32.  The workspace holds the per-query-tile list of kv tiles
+ * to visit (tiles of the block mask that are entirely masked are dropped from it). */
+typedef struct kvax_b200_attn_fwd_params {
+  kvax_b200_attn_shape shape;
+  const void* q; const void* k; const void* v;
+  kvax_b200_block_mask mask;      /* forward mask */
+  void* out;                      /* (B, Sq, Hq, D), strides = shape.o_strides */
+  float* lse;                     /* (B, Hq, Sq) */
+  int32_t* status;                /* optional device int32, must be 0 on entry */
+} kvax_b200_attn_fwd_params;
+
+size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p);
+int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,
+                       kvax_b200_stream_t stream);
+
+/* Backward.  Replaces attn_bwd_preprocess (:373-410, launched :1692-1704),
+ * flash_attention_backward_kernel_dquery (:620-871, launched :1740-1766) and
+ * flash_attention_backward_kernel_dkdv (:874-1191, launched :1778-1807), plus the
+ * GQA group sum (:1855-1868).  dk/dv are fp32 (B, Skv, Hkv, D) contiguous, already
+ * summed over the query heads of each group, as the reference returns them before the
+ * context-parallel reduction; dq is in the input dtype with shape.q_strides. */
+typedef struct kvax_b200_attn_bwd_params {
+  kvax_b200_attn_shape shape;
+  const void* q; const void* k; const void* v;
+  const void* out; const void* dout;   /* strides = shape.o_strides for both */
+  const float* lse;                    /* (B, Hq, Sq) from the forward */
+  kvax_b200_block_mask mask_dq;        /* one row per query block */
+  kvax_b200_block_mask mask_dkdv;      /* one row per kv block    */
+  void* dq;                            /* (B, Sq, Hq, D) input dtype, strides = q_strides */
+  float* dk;                           /* (B, Skv, Hkv, D) fp32 contiguous */
+  float* dv;                           /* (B, Skv, Hkv, D) fp32 contiguous */
+  int32_t* status;
+} kvax_b200_attn_bwd_params;
+
+size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p);
+int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* workspace, size_t workspace_bytes,
+                       kvax_b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVAX_B200_H_ */

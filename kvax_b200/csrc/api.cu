@@ -1,0 +1,162 @@
+// C-ABI layer: argument checks, workspace layout, TMA tensor maps, launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <string.h>
+
+#include "../../include/kvax_b200.h"
+#include "internal.h"
+
+namespace {
+
+using namespace kvx;
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library does not
+// link against libcuda (it has to load on machines without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// bf16 tensor (batch, seq, heads, D) with element strides {batch, seq, head}; boxes of
+// 128 rows x 64 columns of one head, 128-byte swizzle, out-of-range rows read as zero.
+int make_tmap(CUtensorMap* map, const void* base, int batch, int seq, int heads, int d, const int64_t* strides) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return KVAX_B200_ENODEVICE;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((strides[0] | strides[1] | strides[2]) & 7)) return KVAX_B200_EUNSUPPORTED;
+  cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
+  cuuint64_t gstr[3] = {cuuint64_t(strides[2]) * 2, cuuint64_t(strides[1]) * 2, cuuint64_t(strides[0]) * 2};
+  cuuint32_t box[4] = {64, 1, cuuint32_t(kTile), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
+int check_shape(const kvax_b200_attn_shape& s) {
+  if (s.batch <= 0 || s.q_len <= 0 || s.kv_len <= 0 || s.q_heads <= 0 || s.kv_heads <= 0) return KVAX_B200_EINVAL;
+  if (s.q_heads % s.kv_heads) return KVAX_B200_EINVAL;
+  if (s.dtype != KVAX_B200_BF16) return KVAX_B200_EUNSUPPORTED;
+  if (s.head_dim != 64 && s.head_dim != 128) return KVAX_B200_EUNSUPPORTED;
+  if (!s.q_segment_ids || !s.kv_segment_ids) return KVAX_B200_EINVAL;
+  if (!s.assume_sequential_positions && (!s.q_positions || !s.kv_positions)) return KVAX_B200_EINVAL;
+  if (!(s.scale > 0.f) || !isfinite(s.scale)) return KVAX_B200_EUNSUPPORTED;
+  return KVAX_B200_OK;
+}
+
+TokenInfo token_info(const kvax_b200_attn_shape& s) {
+  TokenInfo t;
+  t.q_pos = s.q_positions; t.q_seg = s.q_segment_ids; t.kv_pos = s.kv_positions; t.kv_seg = s.kv_segment_ids;
+  t.q_len = s.q_len; t.kv_len = s.kv_len;
+  t.sequential = s.assume_sequential_positions ? 1 : 0;
+  t.off_first = s.q_global_offset_first; t.off_second = s.q_global_offset_second;
+  return t;
+}
+
+int mask_view(const kvax_b200_block_mask& m, bool kv_outer, int q_len, int kv_len, MaskView* v) {
+  if (!m.lower || !m.upper || !m.lower_full || !m.upper_full || m.q_block <= 0 || m.kv_block <= 0) return KVAX_B200_EINVAL;
+  v->lower = m.lower; v->upper = m.upper; v->lower_full = m.lower_full; v->upper_full = m.upper_full;
+  v->outer_block = kv_outer ? m.kv_block : m.q_block;
+  v->inner_block = kv_outer ? m.q_block : m.kv_block;
+  v->n_outer = kv_outer ? cdiv(kv_len, m.kv_block) : cdiv(q_len, m.q_block);
+  return KVAX_B200_OK;
+}
+
+struct ListLayout { size_t tiles_off, counts_off, total; int n_outer, n_inner; };
+
+ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base) {
+  ListLayout l;
+  l.n_outer = cdiv(outer_len, kTile); l.n_inner = cdiv(inner_len, kTile);
+  l.tiles_off = base;
+  l.counts_off = l.tiles_off + align256(size_t(batch) * l.n_outer * l.n_inner * sizeof(uint32_t));
+  l.total = l.counts_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
+  return l;
+}
+
+}  // namespace
+
+extern "C" const char* kvax_b200_version(void) { return "kvax_b200 0.1 (sm_100a)"; }
+
+extern "C" const char* kvax_b200_error_string(int code) {
+  switch (code) {
+    case KVAX_B200_OK: return "ok";
+    case KVAX_B200_EINVAL: return "invalid argument";
+    case KVAX_B200_EUNSUPPORTED: return "unsupported shape, dtype or alignment";
+    case KVAX_B200_EWORKSPACE: return "workspace too small or misaligned";
+    case KVAX_B200_ELAUNCH: return "CUDA launch or tensor-map creation failed";
+    case KVAX_B200_ENODEVICE: return "no usable device or driver entry point";
+    default: return "unknown error";
+  }
+}
+
+extern "C" size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p) {
+  if (!p || check_shape(p->shape) != KVAX_B200_OK) return 0;
+  return list_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, 0).total;
+}
+
+extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,
+                                  kvax_b200_stream_t stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->out || !p->lse) return KVAX_B200_EINVAL;
+  const kvax_b200_attn_shape& s = p->shape;
+  int rc = check_shape(s);
+  if (rc) return rc;
+  const ListLayout ll = list_layout(s.batch, s.q_len, s.kv_len, 0);
+  if (!workspace || workspace_bytes < ll.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
+  if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2]) & 7 || (reinterpret_cast<uintptr_t>(p->out) & 15)) return KVAX_B200_EUNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+
+  MaskView mv;
+  rc = mask_view(p->mask, false, s.q_len, s.kv_len, &mv);
+  if (rc) return rc;
+
+  ScheduleArgs sa;
+  sa.mask = mv; sa.tok = token_info(s);
+  sa.tiles = reinterpret_cast<uint32_t*>(ws + ll.tiles_off);
+  sa.counts = reinterpret_cast<int32_t*>(ws + ll.counts_off);
+  sa.n_outer_tiles = ll.n_outer; sa.n_inner_tiles = ll.n_inner;
+  sa.outer_len = s.q_len; sa.inner_len = s.kv_len;
+  launch_schedule(false, sa, s.batch, st);
+  if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
+
+  FwdLaunch L;
+  rc = make_tmap(&L.tmap_q, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);  if (rc) return rc;
+  rc = make_tmap(&L.tmap_k, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides); if (rc) return rc;
+  rc = make_tmap(&L.tmap_v, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides); if (rc) return rc;
+  FwdArgs& a = L.args;
+  a.list.tiles = sa.tiles; a.list.counts = sa.counts;
+  a.list.n_outer_tiles = ll.n_outer; a.list.n_inner_tiles = ll.n_inner;
+  a.mask = mv; a.tok = sa.tok;
+  a.out = static_cast<__nv_bfloat16*>(p->out); a.lse = p->lse; a.status = p->status;
+  for (int i = 0; i < 3; ++i) a.o_strides[i] = s.o_strides[i];
+  a.scale_log2e = s.scale * 1.4426950408889634f;
+  a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads;
+  L.batch = s.batch; L.head_dim = s.head_dim;
+  return launch_attn_fwd(L, st);
+}
+
+extern "C" size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p) {
+  (void)p;
+  return 0;
+}
+
+extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* workspace, size_t workspace_bytes,
+                                  kvax_b200_stream_t stream) {
+  (void)p; (void)workspace; (void)workspace_bytes; (void)stream;
+  return KVAX_B200_EUNSUPPORTED;
+}

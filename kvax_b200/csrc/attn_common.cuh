@@ -1,0 +1,83 @@
+// Shared pieces of the attention kernels: the element-level mask rule derived from the
+// block-mask arrays, tile-list encoding, and kernel argument structs.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kvax_b200.h"
+
+namespace kvx {
+
+constexpr int kTile = 128;                 // native tile edge of every attention kernel
+constexpr uint32_t kPartialBit = 0x80000000u;
+
+// Block mask plus the geometry needed to read it.
+struct MaskView {
+  const int32_t* lower;
+  const int32_t* upper;
+  const int32_t* lower_full;
+  const int32_t* upper_full;
+  int32_t outer_block;   // block size on the axis the mask has one row per block of
+  int32_t inner_block;   // block size on the axis the bounds index
+  int32_t n_outer;       // blocks per batch row
+};
+
+// Position / segment arrays of both sides.
+struct TokenInfo {
+  const int32_t* q_pos; const int32_t* q_seg;
+  const int32_t* kv_pos; const int32_t* kv_seg;
+  int32_t q_len, kv_len;
+  int32_t sequential;         // assume_sequential_positions
+  int32_t off_first, off_second;  // global offsets of the two halves of the local queries
+};
+
+// Bounds of one outer row, in tokens of the inner axis.
+struct RowBounds { int lo, lof, uf, up; };
+
+__device__ __forceinline__ RowBounds load_bounds(const MaskView& m, int b, int outer_token) {
+  int blk = outer_token / m.outer_block;
+  blk = min(blk, m.n_outer - 1);
+  const long long o = (long long)b * m.n_outer + blk;
+  RowBounds r;
+  r.lo = __ldg(m.lower + o) * m.inner_block;
+  r.lof = __ldg(m.lower_full + o) * m.inner_block;
+  r.uf = __ldg(m.upper_full + o) * m.inner_block;
+  r.up = __ldg(m.upper + o) * m.inner_block;
+  return r;
+}
+
+// Query position used by the causal test.  With assume_sequential_positions the
+// reference compares global indices: local index plus the offset of the half of the
+// local sequence the token lies in (flash_attention_triton.py:101-108, 1426-1447).
+__device__ __forceinline__ int query_position(const TokenInfo& t, int b, int r) {
+  if (t.sequential) return r + ((2 * r >= t.q_len) ? t.off_second : t.off_first);
+  return __ldg(t.q_pos + (long long)b * t.q_len + r);
+}
+
+// The reference visits inner blocks in three classes (flash_attention_triton.py:292-364
+// for query-outer masks, :1067-1167 for the kv-outer mask):
+//   [lo, lof)  "left"  : segment mask only   (kv-outer: causal AND segment)
+//   [lof, uf)  "full"  : no mask
+//   [uf, up)   "right" : causal AND segment  (kv-outer: segment only)
+// `i` is the token index on the inner axis.  `seg_eq`: raw segment ids equal (PAD
+// matches PAD, :32-41).  `causal`: query position >= kv position.
+template <bool kKvOuter>
+__device__ __forceinline__ bool element_allowed(const RowBounds& rb, int i, bool seg_eq, bool causal) {
+  const bool in_left = (i >= rb.lo) && (i < rb.lof);
+  const bool in_full = (i >= rb.lof) && (i < rb.uf);
+  const bool in_right = (i >= rb.uf) && (i < rb.up);
+  if (kKvOuter) return in_full || (seg_eq && (in_right || (in_left && causal)));
+  return in_full || (seg_eq && (in_left || (in_right && causal)));
+}
+
+// ---------------------------------------------------------------------------
+// Tile lists (built by schedule.cu): for every (batch, outer tile) the inner tiles to
+// visit, ascending; bit 31 marks tiles that need the element-level mask.
+// ---------------------------------------------------------------------------
+struct TileList {
+  const uint32_t* tiles;   // (B, n_outer_tiles, n_inner_tiles)
+  const int32_t* counts;   // (B, n_outer_tiles)
+  int32_t n_outer_tiles, n_inner_tiles;
+};
+
+}  // namespace kvx

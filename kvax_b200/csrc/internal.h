@@ -1,0 +1,41 @@
+// Internal launch interfaces between the C-ABI layer (api.cu) and the kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "attn_common.cuh"
+
+namespace kvx {
+
+struct ScheduleArgs {
+  MaskView mask;
+  TokenInfo tok;
+  uint32_t* tiles;     // (B, n_outer_tiles, n_inner_tiles)
+  int32_t* counts;     // (B, n_outer_tiles)
+  int32_t n_outer_tiles, n_inner_tiles;
+  int32_t outer_len, inner_len;
+};
+void launch_schedule(bool kv_outer, const ScheduleArgs& a, int batch, cudaStream_t s);
+
+struct FwdArgs {
+  TileList list;            // one row per query tile
+  MaskView mask;            // forward mask (query-outer)
+  TokenInfo tok;
+  __nv_bfloat16* out;
+  float* lse;               // (B, Hq, Sq)
+  int32_t* status;
+  long long o_strides[3];   // batch, seq, head (elements)
+  float scale_log2e;
+  int32_t q_heads, group;   // group = Hq / Hkv
+};
+
+struct FwdLaunch {
+  CUtensorMap tmap_q, tmap_k, tmap_v;
+  FwdArgs args;
+  int batch, head_dim;
+};
+int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream);
+
+}  // namespace kvx

@@ -1,0 +1,284 @@
+"""`flash_attention`: document-masked causal GQA attention, forward and backward.
+
+API of kvax/ops/flash_attention_triton.py:2027-2178.  Tensors are torch CUDA tensors in
+the public layout (batch, sequence, heads, head_dim); the kernels read that layout
+directly through strided TMA descriptors, so the four layout transposes of the reference
+(:2158-2160, :2176) do not exist here.
+
+Execution model: one process per GPU.  With context parallelism (the query sequence
+axis of `query_specs` names a mesh axis of size > 1) every process passes its own slice
+of the permuted sequence for query, key and value — what a device sees of the
+reference's global arrays — and the full, un-permuted kv positions / segment ids.  The
+op all-gathers K and V over NCCL into natural order, runs the kernels on the local
+queries, and in the backward pass reduce-scatters fp32 dK/dV back to their owners before
+casting to the input dtype (the reference keeps fp32 through that reduction,
+flash_attention_triton.py:2107-2115).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from kvax_b200 import _lib
+from kvax_b200.utils.common import FlashAttentionParamsConfig, get_default_flash_attention_params
+from kvax_b200.utils.sharding import Mesh, _check_mesh_or_get_global, get_query_context_mesh_axis_name
+from kvax_b200.utils.typing import AttentionMask
+
+_SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 192, 256)   # what the reference accepts
+_KERNEL_HEAD_DIMS = (64, 128)                         # what the sm_100a kernels cover today
+
+
+def _i32(x):
+    return x.to(torch.int32).contiguous()
+
+
+def _block_mask(mask: AttentionMask, q_block: int, kv_block: int) -> tuple[_lib.BlockMask, list]:
+    keep = [t.to(torch.int32).contiguous() for t in mask.flatten()]
+    bm = _lib.BlockMask()
+    bm.lower, bm.upper, bm.lower_full, bm.upper_full = (t.data_ptr() for t in keep)
+    bm.q_block, bm.kv_block = int(q_block), int(kv_block)
+    return bm, keep
+
+
+def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, scale, sequential, offsets):
+    B, Sq, Hq, D = q.shape
+    s.batch, s.q_len, s.kv_len = B, Sq, k.shape[1]
+    s.q_heads, s.kv_heads, s.head_dim = Hq, k.shape[2], D
+    s.dtype = 0
+    s.assume_sequential_positions = int(bool(sequential))
+    s.scale = float(scale)
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
+        if t.stride(3) != 1:
+            raise AssertionError("head_dim must be contiguous")
+        arr = getattr(s, name)
+        arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
+    s.q_positions, s.q_segment_ids = q_pos.data_ptr(), q_seg.data_ptr()
+    s.kv_positions, s.kv_segment_ids = kv_pos.data_ptr(), kv_seg.data_ptr()
+    s.q_global_offset_first, s.q_global_offset_second = offsets
+
+
+def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: AttentionMask, fwd_blocks, scale,
+                      assume_sequential_positions=False, offsets=(0, 0)):
+    """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2) with lse2 (B, Hq, Sq)
+    fp32, the base-2 log-sum-exp of the scaled scores."""
+    lib = _lib.load()
+    B, Sq, Hq, D = q.shape
+    out = torch.empty_like(q)
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    p = _lib.AttnFwdParams()
+    _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)
+    p.out, p.lse, p.status = out.data_ptr(), lse.data_ptr(), status.data_ptr()
+    ws_bytes = lib.kvax_b200_attn_fwd_workspace_bytes(p)
+    if ws_bytes == 0:
+        raise _lib.KvaxB200Error("kvax_b200_attn_fwd_workspace_bytes rejected the arguments "
+                                 f"(head_dim={D}, dtype={q.dtype})")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.kvax_b200_attn_fwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "kvax_b200_attn_fwd")
+    return out, lse, status
+
+
+def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, mask_dq: AttentionMask,
+                       mask_dkdv: AttentionMask, bwd_blocks, scale, assume_sequential_positions=False,
+                       offsets=(0, 0)):
+    """Direct wrapper of kvax_b200_attn_bwd.  Returns (dq in the input dtype, dk fp32,
+    dv fp32); dk/dv are summed over the query heads of each kv head."""
+    lib = _lib.load()
+    dq = torch.empty_like(q)
+    dk = torch.empty(k.shape, dtype=torch.float32, device=k.device)
+    dv = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    p = _lib.AttnBwdParams()
+    if out.stride() != dout.stride():
+        dout = dout.contiguous()
+        out = out.contiguous()
+    _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
+    p.q, p.k, p.v, p.out, p.dout, p.lse = (t.data_ptr() for t in (q, k, v, out, dout, lse))
+    bq, bk = bwd_blocks
+    p.mask_dq, keep1 = _block_mask(mask_dq, bk, bq)        # dq mask: block sizes swapped
+    p.mask_dkdv, keep2 = _block_mask(mask_dkdv, bq, bk)
+    p.dq, p.dk, p.dv, p.status = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), status.data_ptr()
+    ws_bytes = lib.kvax_b200_attn_bwd_workspace_bytes(p)
+    if ws_bytes == 0:
+        raise _lib.KvaxB200Error("kvax_b200_attn_bwd_workspace_bytes rejected the arguments")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.kvax_b200_attn_bwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(rc, "kvax_b200_attn_bwd")
+    return dq, dk, dv, status
+
+
+def check_status(status: torch.Tensor, what: str) -> None:
+    """Reads the device status word (synchronises) and raises on a device-side failure."""
+    code = int(status.item())
+    if code != 0:
+        raise _lib.KvaxB200Error(f"{what}: device status {code} (a bounded wait gave up; 100 + barrier id)")
+
+
+def context_offsets(rank: int, cp: int, local_q_len: int, permuted: bool) -> tuple[int, int]:
+    """Global index of local query token 0 and the amount to add to local indices of the
+    second half of the local queries (flash_attention_triton.py:1426-1447): with the
+    load-balancing permutation rank r holds chunk r followed by chunk 2CP-1-r."""
+    if cp == 1:
+        return (0, 0)
+    if not permuted:
+        return (rank * local_q_len, rank * local_q_len)
+    half = local_q_len // 2
+    return (rank * half, (2 * cp - rank - 1) * half - half)
+
+
+def _gather_kv(x: torch.Tensor, cp: int, group, permuted: bool) -> torch.Tensor:
+    """All-gather of the local (B, S_loc, H, D) slices into (B, S, H, D) in natural order."""
+    import torch.distributed as dist
+    from kvax_b200.utils.permutation import _permute_one
+
+    x = x.contiguous()
+    B = x.shape[0]
+    gathered = torch.empty((cp,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(gathered, x, group=group)
+    if B == 1:
+        full = gathered.view(1, cp * x.shape[1], *x.shape[2:])
+    else:
+        full = gathered.transpose(0, 1).contiguous().view(B, cp * x.shape[1], *x.shape[2:])
+    return _permute_one(full, cp, reverse=True) if permuted else full
+
+
+def _scatter_dkv(g: torch.Tensor, cp: int, group, permuted: bool, out_dtype) -> torch.Tensor:
+    """Reduce-scatter (fp32 sum) of a natural-order (B, S, H, D) gradient to the slice each
+    rank owns, then the cast to the input dtype."""
+    import torch.distributed as dist
+    from kvax_b200.utils.permutation import _permute_one
+
+    B, S = g.shape[:2]
+    if permuted:
+        g = _permute_one(g, cp, reverse=False)
+    g = g.view(B, cp, S // cp, *g.shape[2:])
+    if B != 1:
+        g = g.transpose(0, 1).contiguous()
+    g = g.reshape(cp, B, S // cp, *g.shape[3:])
+    local = torch.empty(g.shape[1:], dtype=g.dtype, device=g.device)
+    dist.reduce_scatter_tensor(local, g, op=dist.ReduceOp.SUM, group=group)
+    return local.to(out_dtype)
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, masks, scale, fwd_params, bwd_params,
+                sequential, permuted, cp, rank, group):
+        if cp > 1:
+            k_full = _gather_kv(key, cp, group, permuted)
+            v_full = _gather_kv(value, cp, group, permuted)
+        else:
+            k_full, v_full = key, value
+        offsets = context_offsets(rank, cp, query.shape[1], permuted)
+        out, lse, status = attention_forward(
+            query, k_full, v_full, q_pos, q_seg, kv_pos, kv_seg, masks[0],
+            (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, offsets)
+        ctx.save_for_backward(query, k_full, v_full, out, lse, q_pos, q_seg, kv_pos, kv_seg,
+                              *[t for m in masks for t in m.flatten()])
+        ctx.n_masks = len(masks)
+        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, offsets, key.dtype)
+        ctx.status = status
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        saved = ctx.saved_tensors
+        query, k_full, v_full, out, lse, q_pos, q_seg, kv_pos, kv_seg = saved[:9]
+        flat = saved[9:]
+        if ctx.n_masks != 3:
+            raise ValueError("Length of mask_tensors should be equal to two")
+        masks = [AttentionMask.unflatten(flat[4 * i:4 * i + 4]) for i in range(3)]
+        scale, bwd_params, sequential, permuted, cp, group, offsets, kv_dtype = ctx.cfg
+        bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
+        if query.shape[1] % bq or k_full.shape[1] % bk:
+            raise AssertionError("sequence lengths must be divisible by the backward block sizes")
+        dq, dk, dv, _ = attention_backward(query, k_full, v_full, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg,
+                                           masks[1], masks[2], (bq, bk), scale, sequential, offsets)
+        if cp > 1:
+            dk = _scatter_dkv(dk, cp, group, permuted, kv_dtype)
+            dv = _scatter_dkv(dv, cp, group, permuted, kv_dtype)
+        else:
+            dk, dv = dk.to(kv_dtype), dv.to(kv_dtype)
+        return (dq, dk, dv) + (None,) * 13
+
+
+def flash_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_positions: torch.Tensor,
+    query_segment_ids: torch.Tensor,
+    kv_positions: torch.Tensor,
+    kv_segment_ids: torch.Tensor,
+    mask: tuple[AttentionMask, ...],
+    scale: float = 1.0,
+    bias: torch.Tensor | None = None,
+    fwd_params: FlashAttentionParamsConfig | None = None,
+    bwd_params: FlashAttentionParamsConfig | None = None,
+    assume_sequential_positions: bool = False,
+    memory_optimized_gqa_backward: bool = False,
+    permute_tokens_for_load_balance: bool = True,
+    debug: bool = False,
+    mesh: Mesh | None = None,
+) -> torch.Tensor:
+    """Attention output of shape (batch, query_seq, heads, head_dim), differentiable with
+    respect to query, key and value.
+
+    `mask` is the tuple returned by `create_attention_mask` (one mask for inference, three
+    for training); `fwd_params` / `bwd_params` must be the block sizes those masks were
+    built with.  `memory_optimized_gqa_backward` is accepted and has no effect: the dK/dV
+    kernel always accumulates the query heads of a group on chip.  `debug` is accepted and
+    ignored.  Raises NotImplementedError for `bias`, ValueError for a missing mesh / specs
+    or an empty mask tuple, AssertionError for shape errors, as the reference does.
+    """
+    mesh = _check_mesh_or_get_global(mesh)
+    axis = get_query_context_mesh_axis_name(mesh)
+    if bias is not None:
+        raise NotImplementedError("Bias is not supported in Flash multi head attention")
+    if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:
+        raise AssertionError("query, key and value must have rank 4")
+    if query.shape[-1] not in _SUPPORTED_HEAD_DIMS:
+        raise AssertionError(f"Attention hid_dim can take values {list(_SUPPORTED_HEAD_DIMS)}")
+    if mask is None or len(mask) == 0:
+        raise ValueError("Length of mask_tensors should be at least equal to one")
+    if len(mask) not in (1, 3):
+        raise ValueError(f"The case with num_mask_tensors={len(mask)} is not supported.")
+    if not query.is_cuda:
+        raise _lib.KvaxB200Error("flash_attention needs CUDA tensors (there is no CPU fallback)")
+    if query.dtype != torch.bfloat16 or query.shape[-1] not in _KERNEL_HEAD_DIMS or value.shape[-1] != query.shape[-1]:
+        raise _lib.KvaxB200Error(
+            f"the sm_100a kernels cover bf16 with head_dim in {_KERNEL_HEAD_DIMS} and Dqk == Dv; "
+            f"got {query.dtype}, Dqk={query.shape[-1]}, Dv={value.shape[-1]}")
+    B, Sq, Hq, _ = query.shape
+    if key.shape[0] != B or value.shape[:3] != key.shape[:3] or Hq % key.shape[2]:
+        raise AssertionError("inconsistent query / key / value shapes")
+    if fwd_params is None:
+        fwd_params = get_default_flash_attention_params(backward=False)
+    if bwd_params is None:
+        bwd_params = get_default_flash_attention_params(backward=True)
+
+    cp, rank, group = 1, 0, None
+    if axis is not None:
+        if axis not in mesh.shape:
+            raise ValueError(f"Mesh axis {axis} is not present in the device mesh shape.")
+        cp = mesh.shape[axis]
+        rank = mesh.coordinate(axis)
+        group = mesh.group(axis) if cp > 1 else None
+    if cp > 1 and Sq % fwd_params.query_block_size:
+        raise AssertionError("with context parallelism the local query length must be a multiple of the block size")
+    kv_len = key.shape[1] * cp
+    if tuple(query_positions.shape) != (B, Sq) or tuple(query_segment_ids.shape) != (B, Sq):
+        raise AssertionError("query positions / segment ids must have shape (batch, query_seq)")
+    if tuple(kv_positions.shape) != (B, kv_len) or tuple(kv_segment_ids.shape) != (B, kv_len):
+        raise AssertionError("kv positions / segment ids must have shape (batch, kv_seq)")
+
+    return _FlashAttention.apply(
+        query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
+        _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
+        bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)

@@ -1,0 +1,112 @@
+"""CPU oracle for document-masked causal GQA attention.  TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the CPU-baseline / reference arm of the benchmark
+may import this module; the product path never does.
+
+Restates the dense masked attention the reference's tests compare their kernels with:
+  tests/test_attention.py:33-49            dense mask = (q_seg == kv_seg) & (q_pos >= kv_pos)
+  kvax/ops/flash_attention_cudnn.py:14-24  segment mask
+  kvax/ops/flash_attention_cudnn.py:91-113 softmax(scale * Q K^T + mask) V with KV heads
+                                           shared by Hq/Hkv query heads
+The dense op itself is jax.nn.dot_product_attention (third-party, jax>=0.4.34 per the
+reference's pyproject.toml, not vendored and not installed here) so its published
+definition is restated.  The reference holds no golden vectors for attention outputs
+(its tests compare two GPU implementations): PARITY UNPINNED for this module, other
+than through the analytic gradient check in tests/test_oracle_attention.py.
+
+Layouts follow the public API: q (B, Sq, Hq, D), k/v (B, Skv, Hkv, D).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+PADDING_SEGMENT_ID = -1
+
+
+def _mask(q_pos, q_seg, kv_pos, kv_seg):
+    return (q_seg[:, :, None] == kv_seg[:, None, :]) & (q_pos[:, :, None] >= kv_pos[:, None, :])
+
+
+def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, scale, dtype=np.float64):
+    """Returns (out (B,Sq,Hq,Dv), lse2 (B,Hq,Sq)) — lse2 is the base-2 log-sum-exp of
+    the scaled scores, the quantity the reference's forward kernel stores
+    (flash_attention_triton.py:366-369).  Rows with no unmasked key give out=0."""
+    q = np.asarray(q, dtype); k = np.asarray(k, dtype); v = np.asarray(v, dtype)
+    B, Sq, Hq, D = q.shape
+    Hkv = k.shape[2]
+    G = Hq // Hkv
+    mask = _mask(np.asarray(q_pos), np.asarray(q_seg), np.asarray(kv_pos), np.asarray(kv_seg))
+    out = np.zeros((B, Sq, Hq, v.shape[3]), dtype)
+    lse2 = np.zeros((B, Hq, Sq), dtype)
+    for b in range(B):
+        for h in range(Hq):
+            s = (q[b, :, h] @ k[b, :, h // G].T) * scale
+            s = np.where(mask[b], s, -np.inf)
+            m = s.max(-1, keepdims=True)
+            m = np.where(np.isfinite(m), m, 0.0)
+            p = np.exp(s - m)
+            l = p.sum(-1, keepdims=True)
+            safe = np.where(l > 0, l, 1.0)
+            out[b, :, h] = (p / safe) @ v[b, :, h // G]
+            with np.errstate(divide="ignore"):
+                lse2[b, h] = ((m + np.log(safe)) / np.log(2.0))[:, 0]
+            lse2[b, h] = np.where(l[:, 0] > 0, lse2[b, h], np.inf)
+    return out, lse2
+
+
+def attention_backward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, scale, dout, dtype=np.float64):
+    """Analytic gradients of sum(out * dout) w.r.t. q, k, v (GQA: dk/dv summed over the
+    query heads of a group, as flash_attention_triton.py:1855-1868 does)."""
+    q = np.asarray(q, dtype); k = np.asarray(k, dtype); v = np.asarray(v, dtype)
+    dout = np.asarray(dout, dtype)
+    B, Sq, Hq, D = q.shape
+    Hkv = k.shape[2]
+    G = Hq // Hkv
+    mask = _mask(np.asarray(q_pos), np.asarray(q_seg), np.asarray(kv_pos), np.asarray(kv_seg))
+    dq = np.zeros_like(q); dk = np.zeros_like(k); dv = np.zeros_like(v)
+    for b in range(B):
+        for h in range(Hq):
+            g = h // G
+            s = (q[b, :, h] @ k[b, :, g].T) * scale
+            s = np.where(mask[b], s, -np.inf)
+            m = s.max(-1, keepdims=True)
+            m = np.where(np.isfinite(m), m, 0.0)
+            p = np.exp(s - m)
+            l = p.sum(-1, keepdims=True)
+            p = p / np.where(l > 0, l, 1.0)
+            do = dout[b, :, h]
+            dv[b, :, g] += p.T @ do
+            dp = do @ v[b, :, g].T
+            delta = (p * dp).sum(-1, keepdims=True)
+            ds = p * (dp - delta) * scale
+            dq[b, :, h] = ds @ k[b, :, g]
+            dk[b, :, g] += ds.T @ q[b, :, h]
+    return dq, dk, dv
+
+
+def attention_fwd_bwd_torch(q, k, v, q_pos, q_seg, kv_pos, kv_seg, scale, dout, heads_chunk=None):
+    """Same computation with torch CPU ops (multi-threaded fp32) — the timed CPU baseline.
+    Returns (out, dq, dk, dv) as torch tensors."""
+    import torch
+
+    q = torch.as_tensor(q, dtype=torch.float32).requires_grad_(True)
+    k = torch.as_tensor(k, dtype=torch.float32).requires_grad_(True)
+    v = torch.as_tensor(v, dtype=torch.float32).requires_grad_(True)
+    dout = torch.as_tensor(dout, dtype=torch.float32)
+    B, Sq, Hq, D = q.shape
+    G = Hq // k.shape[2]
+    q_pos = torch.as_tensor(q_pos); kv_pos = torch.as_tensor(kv_pos)
+    q_seg = torch.as_tensor(q_seg); kv_seg = torch.as_tensor(kv_seg)
+    mask = (q_seg[:, :, None] == kv_seg[:, None, :]) & (q_pos[:, :, None] >= kv_pos[:, None, :])
+    kk = k.repeat_interleave(G, dim=2)
+    vv = v.repeat_interleave(G, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q, kk) * scale
+    s = s.masked_fill(~mask[:, None], float("-inf"))
+    rowmax = s.amax(-1, keepdim=True)
+    rowmax = torch.where(torch.isfinite(rowmax), rowmax, torch.zeros_like(rowmax))
+    p = torch.exp(s - rowmax)
+    l = p.sum(-1, keepdim=True)
+    p = p / torch.where(l > 0, l, torch.ones_like(l))
+    out = torch.einsum("bhqk,bkhd->bqhd", p, vv)
+    (out * dout).sum().backward()
+    return out.detach(), q.grad, k.grad, v.grad

@@ -1,0 +1,43 @@
+"""Shared helpers of the GPU parity tests."""
+import numpy as np
+import torch
+
+from oracle import attention_oracle as ao
+
+# Tolerances of the north-star statement: fp32 comparison of bf16 results.
+MAX_ABS = 2e-2
+REL_L2 = 5e-3
+
+
+def to_bf16_cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).cuda()
+
+
+def bf16_round(a):
+    """What the kernels actually see: inputs rounded to bf16, as fp32 NumPy."""
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+def i32_cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.int32).cuda()
+
+
+def compare(name, got, ref, row_mask=None, max_abs=MAX_ABS, rel_l2=REL_L2):
+    """got / ref: float arrays; row_mask (broadcastable) selects rows that are specified
+    (non-PAD tokens).  Returns a dict of metrics; raises AssertionError beyond tolerance."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    if row_mask is not None:
+        got = np.where(row_mask, got, 0.0)
+        ref = np.where(row_mask, ref, 0.0)
+    assert np.isfinite(got).all(), f"{name}: non-finite values"
+    err = np.abs(got - ref).max()
+    rel = np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)
+    assert err <= max_abs and rel <= rel_l2, f"{name}: max-abs {err:.4g} (<= {max_abs}), rel-L2 {rel:.4g} (<= {rel_l2}), |ref|max {np.abs(ref).max():.3g}"
+    return dict(max_abs=err, rel_l2=rel)
+
+
+def oracle_fwd(inp, q=None, k=None, v=None):
+    p, s = inp["positions"], inp["segment_ids"]
+    return ao.attention_forward(bf16_round(inp["q"]), bf16_round(inp["k"]), bf16_round(inp["v"]),
+                                p, s, p, s, inp["scale"], dtype=np.float32)
