@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvax_b200.so")
-SOURCES = ["api.cu", "mask_build.cu", "permute.cu", "schedule.cu", "attn_fwd.cu"]
+SOURCES = ["api.cu", "mask_build.cu", "permute.cu", "schedule.cu", "attn_fwd.cu", "attn_bwd.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",

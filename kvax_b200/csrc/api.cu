@@ -150,13 +150,87 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   return launch_attn_fwd(L, st);
 }
 
+namespace {
+
+struct BwdLayout { ListLayout dq, dkdv; size_t delta_off, total; };
+
+BwdLayout bwd_layout(const kvax_b200_attn_shape& s) {
+  BwdLayout l;
+  l.dq = list_layout(s.batch, s.q_len, s.kv_len, 0);
+  l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total);
+  l.delta_off = l.dkdv.total;
+  l.total = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));
+  return l;
+}
+
+}  // namespace
+
 extern "C" size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p) {
-  (void)p;
-  return 0;
+  if (!p || check_shape(p->shape) != KVAX_B200_OK) return 0;
+  return bwd_layout(p->shape).total;
 }
 
 extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* workspace, size_t workspace_bytes,
                                   kvax_b200_stream_t stream) {
-  (void)p; (void)workspace; (void)workspace_bytes; (void)stream;
-  return KVAX_B200_EUNSUPPORTED;
+  if (!p || !p->q || !p->k || !p->v || !p->out || !p->dout || !p->lse || !p->dq || !p->dk || !p->dv) return KVAX_B200_EINVAL;
+  const kvax_b200_attn_shape& s = p->shape;
+  int rc = check_shape(s);
+  if (rc) return rc;
+  const BwdLayout bl = bwd_layout(s);
+  if (!workspace || workspace_bytes < bl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
+  if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2] | s.q_strides[0] | s.q_strides[1] | s.q_strides[2]) & 7) return KVAX_B200_EUNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(p->dq) | reinterpret_cast<uintptr_t>(p->dk) | reinterpret_cast<uintptr_t>(p->dv) |
+       reinterpret_cast<uintptr_t>(p->out) | reinterpret_cast<uintptr_t>(p->dout)) & 15) return KVAX_B200_EUNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  float* delta = reinterpret_cast<float*>(ws + bl.delta_off);
+  const TokenInfo tok = token_info(s);
+
+  MaskView mv_dq, mv_dkdv;
+  rc = mask_view(p->mask_dq, false, s.q_len, s.kv_len, &mv_dq);     if (rc) return rc;
+  rc = mask_view(p->mask_dkdv, true, s.q_len, s.kv_len, &mv_dkdv);  if (rc) return rc;
+
+  ScheduleArgs sq;
+  sq.mask = mv_dq; sq.tok = tok;
+  sq.tiles = reinterpret_cast<uint32_t*>(ws + bl.dq.tiles_off); sq.counts = reinterpret_cast<int32_t*>(ws + bl.dq.counts_off);
+  sq.n_outer_tiles = bl.dq.n_outer; sq.n_inner_tiles = bl.dq.n_inner; sq.outer_len = s.q_len; sq.inner_len = s.kv_len;
+  launch_schedule(false, sq, s.batch, st);
+  ScheduleArgs sk;
+  sk.mask = mv_dkdv; sk.tok = tok;
+  sk.tiles = reinterpret_cast<uint32_t*>(ws + bl.dkdv.tiles_off); sk.counts = reinterpret_cast<int32_t*>(ws + bl.dkdv.counts_off);
+  sk.n_outer_tiles = bl.dkdv.n_outer; sk.n_inner_tiles = bl.dkdv.n_inner; sk.outer_len = s.kv_len; sk.inner_len = s.q_len;
+  launch_schedule(true, sk, s.batch, st);
+  if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
+
+  long long ostr[3] = {s.o_strides[0], s.o_strides[1], s.o_strides[2]};
+  rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
+                             ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
+  if (rc) return rc;
+
+  CUtensorMap tq, tk, tv, tdo;
+  rc = make_tmap(&tq, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);     if (rc) return rc;
+  rc = make_tmap(&tk, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides);   if (rc) return rc;
+  rc = make_tmap(&tv, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides);   if (rc) return rc;
+  rc = make_tmap(&tdo, p->dout, s.batch, s.q_len, s.q_heads, s.head_dim, s.o_strides); if (rc) return rc;
+
+  BwdLaunch L;
+  BwdArgs& a = L.args;
+  a.tok = tok; a.lse = p->lse; a.delta = delta;
+  a.dq = static_cast<__nv_bfloat16*>(p->dq); a.dk = p->dk; a.dv = p->dv; a.status = p->status;
+  for (int i = 0; i < 3; ++i) a.q_strides[i] = s.q_strides[i];
+  a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
+  a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;
+  L.batch = s.batch; L.head_dim = s.head_dim;
+
+  // dQ: resident Q, dO of one query tile; streams K, V
+  a.list.tiles = sq.tiles; a.list.counts = sq.counts; a.list.n_outer_tiles = bl.dq.n_outer; a.list.n_inner_tiles = bl.dq.n_inner;
+  a.mask = mv_dq;
+  L.tmap_x1 = tq; L.tmap_x2 = tdo; L.tmap_y1 = tk; L.tmap_y2 = tv;
+  rc = launch_attn_bwd(L, false, st);
+  if (rc) return rc;
+  // dK/dV: resident K, V of one kv tile; streams Q, dO of every query head of the group
+  a.list.tiles = sk.tiles; a.list.counts = sk.counts; a.list.n_outer_tiles = bl.dkdv.n_outer; a.list.n_inner_tiles = bl.dkdv.n_inner;
+  a.mask = mv_dkdv;
+  L.tmap_x1 = tk; L.tmap_x2 = tv; L.tmap_y1 = tq; L.tmap_y2 = tdo;
+  return launch_attn_bwd(L, true, st);
 }

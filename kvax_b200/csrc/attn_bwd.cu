@@ -1,0 +1,398 @@
+// Flash-attention backward for sm_100a (B200): delta preprocess, dQ kernel, dK/dV kernel.
+//
+// The two main kernels are instances of one template.  An "outer" 128-row tile stays
+// resident in shared memory (dQ kernel: the Q and dO tiles of one query tile and head;
+// dK/dV kernel: the K and V tiles of one kv tile and kv head) while "inner" tiles stream
+// through a two-stage TMA pipeline (dQ kernel: K and V tiles of the list of kv tiles;
+// dK/dV kernel: Q and dO tiles of every query head of the group times the list of query
+// tiles).  Per inner tile:
+//     T1 = X1 * Y1^T   (scores:  Q K^T   or  K Q^T)        tcgen05, both operands smem
+//     T2 = X2 * Y2^T   (dP:      dO V^T  or  V dO^T)       tcgen05, both operands smem
+//     P  = exp2(T1 * scale*log2e - LSE2), masked;  dS = P * (T2 - delta)   (registers)
+//     P, dS -> bf16 -> TMEM over T1, T2
+//     ACC1 += P  * Y2   (dV += P^T dO;  dK/dV kernel only)  tcgen05, A from TMEM
+//     ACC2 += dS * Y1   (dQ += dS K  or  dK += dS^T Q)      tcgen05, A from TMEM
+// Warps 0-3 do the register math (thread t = outer row t = TMEM lane t), warp 4 is the
+// TMA producer, warp 5 issues the MMAs.  The query heads of a GQA group are accumulated
+// on chip by the dK/dV kernel, so dK/dV leave the kernel already summed over the group
+// (the reference sums a (B, Hq, Skv, D) fp32 temporary afterwards,
+// kvax/ops/flash_attention_triton.py:1855-1868).
+//
+// Semantics follow flash_attention_backward_kernel_dquery (:620-871),
+// flash_attention_backward_kernel_dkdv (:874-1191) and attn_bwd_preprocess (:373-410).
+#include "attn_common.cuh"
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace kvx {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+
+enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_TFULL, B_AFULL, B_ACCFULL, B_COUNT };
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kBoxBytes = kTile * 64 * 2;
+  static constexpr int kX1 = 0, kX2 = kTileBytes;
+  static constexpr int kY = 2 * kTileBytes;              // stage s: Y1 at kY + s*2*tile, Y2 right after
+  static constexpr int kCols = 6 * kTileBytes;           // per-column info, 2 buffers x 4 arrays x 128 x 4 B
+  static constexpr int kBars = kCols + 2 * 4 * kTile * 4;
+  static constexpr int kTmemSlot = kBars + 8 * B_COUNT;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kTotal = kAbort + 4 + 1024;
+};
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+template <int D, bool kKvOuter>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_constant__ CUtensorMap tmap_x2,
+                const __grid_constant__ CUtensorMap tmap_y1, const __grid_constant__ CUtensorMap tmap_y2,
+                const BwdArgs a) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbort);
+  int* s_cols = reinterpret_cast<int*>(smem + L::kCols);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int xh = blockIdx.x;                 // dQ: query head; dK/dV: kv head
+  const int ot = blockIdx.y, b = blockIdx.z; // outer tile, batch
+  const int group = a.group;
+  const long long list_row = (long long)b * a.list.n_outer_tiles + ot;
+  const int count = __ldg(a.list.counts + list_row);
+  const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
+  const int n_items = kKvOuter ? count * group : count;
+  const int outer_len = kKvOuter ? a.tok.kv_len : a.tok.q_len;
+  const int inner_len = kKvOuter ? a.tok.q_len : a.tok.kv_len;
+
+  const int r = ot * kTile + tid;            // outer row of a compute thread
+  const bool row_valid = (tid < kTile) && (r < outer_len);
+
+  if (n_items == 0) {                        // no contributing tile: zero gradients
+    if (row_valid) {
+      if (kKvOuter) {
+        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4* dk = reinterpret_cast<float4*>(a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D);
+        float4* dv = reinterpret_cast<float4*>(a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D);
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) { dk[i] = z; dv[i] = z; }
+      } else {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* dq = reinterpret_cast<uint4*>(a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2]);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) dq[i] = z;
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(&bars[i], i == B_AFULL ? kTile : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tT1 = tmem_base, tT2 = tmem_base + kTile;
+  const uint32_t tAcc1 = tmem_base + 2 * kTile, tAcc2 = tmem_base + 3 * kTile;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_x1); prefetch_tmap(&tmap_x2); prefetch_tmap(&tmap_y1); prefetch_tmap(&tmap_y2);
+      mbar_arrive_expect_tx(&bars[B_XFULL], 2 * L::kTileBytes);
+#pragma unroll
+      for (int x = 0; x < D / 64; ++x) {
+        tma_load_4d(smem + L::kX1 + x * L::kBoxBytes, &tmap_x1, &bars[B_XFULL], x * 64, xh, ot * kTile, b);
+        tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_x2, &bars[B_XFULL], x * 64, xh, ot * kTile, b);
+      }
+      bool ok = true;
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i & 1;
+        const int j = kKvOuter ? (i % count) : i;
+        const int yh = kKvOuter ? (xh * group + i / count) : (xh / group);
+        const int u = int(__ldg(list + j) & ~kPartialBit);
+        if (i >= 2) ok = mbar_wait(&bars[B_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, B_YEMPTY0 + st);
+        if (!ok) break;
+        uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
+        uint8_t* y2 = y1 + L::kTileBytes;
+        mbar_arrive_expect_tx(&bars[B_YFULL0 + st], 2 * L::kTileBytes);
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x) {
+          tma_load_4d(y1 + x * L::kBoxBytes, &tmap_y1, &bars[B_YFULL0 + st], x * 64, yh, u * kTile, b);
+          tma_load_4d(y2 + x * L::kBoxBytes, &tmap_y2, &bars[B_YFULL0 + st], x * 64, yh, u * kTile, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
+      const uint32_t x1 = smem_u32(smem + L::kX1), x2 = smem_u32(smem + L::kX2);
+      bool ok = mbar_wait(&bars[B_XFULL], 0, abort_flag, a.status, B_XFULL);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t y1 = smem_u32(smem + L::kY + st * 2 * L::kTileBytes), y2 = y1 + L::kTileBytes;
+        ok = mbar_wait(&bars[B_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_YFULL0 + st);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
+          umma_ss(tT1, make_sdesc_sw128(x1 + off, 16, 1024), make_sdesc_sw128(y1 + off, 16, 1024), idesc_t, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
+          umma_ss(tT2, make_sdesc_sw128(x2 + off, 16, 1024), make_sdesc_sw128(y2 + off, 16, 1024), idesc_t, kk > 0);
+        }
+        umma_commit(&bars[B_TFULL]);
+        ok = mbar_wait(&bars[B_AFULL], i & 1, abort_flag, a.status, B_AFULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc_on = (i > 0) ? 1u : 0u;
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          if (kKvOuter)
+            umma_ts(tAcc1, tT1 + kk * 8, make_sdesc_sw128(y2 + kk * 16 * 128, L::kBoxBytes, 1024), idesc_acc, acc_on | (kk > 0));
+          umma_ts(tAcc2, tT2 + kk * 8, make_sdesc_sw128(y1 + kk * 16 * 128, L::kBoxBytes, 1024), idesc_acc, acc_on | (kk > 0));
+        }
+        umma_commit(&bars[B_YEMPTY0 + st]);
+        if (i == n_items - 1) umma_commit(&bars[B_ACCFULL]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ register math
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const float c = a.scale_log2e;
+    const RowBounds rb = load_bounds(a.mask, b, min(r, outer_len - 1));
+    int o_seg = KVAX_B200_PADDING_SEGMENT_ID, o_pos = 0;
+    float row_lse = 0.f, row_delta = 0.f;
+    if (row_valid) {
+      if (kKvOuter) {
+        o_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
+        o_pos = a.tok.sequential ? r : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + r);
+      } else {
+        o_seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + r);
+        o_pos = query_position(a.tok, b, r);
+        row_lse = __ldg(a.lse + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
+        row_delta = __ldg(a.delta + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
+      }
+    }
+    bool ok = true;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const int j = kKvOuter ? (i % count) : i;
+      const uint32_t e = __ldg(list + j);
+      const int c0 = int(e & ~kPartialBit) * kTile;
+      const bool partial = (e & kPartialBit) != 0;
+      // per-column info of this inner tile: segment id, position (partial tiles only) and,
+      // for the dK/dV kernel, LSE2 and delta of the query rows
+      int* cs = s_cols + (i & 1) * 4 * kTile;
+      {
+        const int col = c0 + tid;
+        int seg = KVAX_B200_PADDING_SEGMENT_ID, pos = 0;
+        float lse = INFINITY, dl = 0.f;
+        if (col < inner_len) {
+          if (kKvOuter) {
+            const int yh = xh * group + i / count;
+            const long long o = ((long long)b * a.q_heads + yh) * a.tok.q_len + col;
+            lse = __ldg(a.lse + o); dl = __ldg(a.delta + o);
+            if (partial) { seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + col); pos = query_position(a.tok, b, col); }
+          } else if (partial) {
+            seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + col);
+            pos = a.tok.sequential ? col : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + col);
+          }
+        }
+        cs[tid] = seg; cs[kTile + tid] = pos;
+        cs[2 * kTile + tid] = __float_as_int(lse); cs[3 * kTile + tid] = __float_as_int(dl);
+      }
+      named_barrier_sync(1, kTile);
+      ok = mbar_wait(&bars[B_TFULL], i & 1, abort_flag, a.status, B_TFULL);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(tT1 + lane_base + ch * 32, s);
+        tmem_ld32(tT2 + lane_base + ch * 32, dp);
+        uint32_t keep = 0xffffffffu;
+        if (partial) {
+          keep = 0;
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int ci = ch * 32 + jj, col = c0 + ci;
+            const bool seg_eq = (cs[ci] == o_seg);
+            const bool causal = kKvOuter ? (cs[kTile + ci] >= o_pos) : (o_pos >= cs[kTile + ci]);
+            const bool al = row_valid && (col < inner_len) && element_allowed<kKvOuter>(rb, col, seg_eq, causal);
+            keep |= (al ? 1u : 0u) << jj;
+          }
+        }
+        tmem_ld_wait(s);
+        tmem_ld_wait(dp);
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          float p[2], ds[2];
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int ci = ch * 32 + jj + t;
+            const float lse = kKvOuter ? __int_as_float(cs[2 * kTile + ci]) : row_lse;
+            const float dl = kKvOuter ? __int_as_float(cs[3 * kTile + ci]) : row_delta;
+            float pv = fast_exp2(fmaf(__uint_as_float(s[jj + t]), c, -lse));
+            pv = ((keep >> (jj + t)) & 1u) ? pv : 0.f;
+            p[t] = pv;
+            ds[t] = pv * (__uint_as_float(dp[jj + t]) - dl);
+          }
+          pk[jj >> 1] = pack_bf16(p[0], p[1]);
+          dk[jj >> 1] = pack_bf16(ds[0], ds[1]);
+        }
+        if (kKvOuter) tmem_st16(tT1 + lane_base + ch * 16, pk);
+        tmem_st16(tT2 + lane_base + ch * 16, dk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[B_AFULL]);
+    }
+
+    if (ok) ok = mbar_wait(&bars[B_ACCFULL], 0, abort_flag, a.status, B_ACCFULL);
+    if (ok) {
+      tc_fence_after();
+      if (kKvOuter) {
+        float* dk = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D;
+        float* dv = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t v1[32], v2[32];
+          tmem_ld32(tAcc1 + lane_base + ch * 32, v1);
+          tmem_ld32(tAcc2 + lane_base + ch * 32, v2);
+          tmem_ld_wait(v1);
+          tmem_ld_wait(v2);
+          if (row_valid) {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 4) {
+              reinterpret_cast<float4*>(dv)[(ch * 32 + jj) >> 2] =
+                  make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
+              reinterpret_cast<float4*>(dk)[(ch * 32 + jj) >> 2] =
+                  make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
+                              __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+            }
+          }
+        }
+      } else {
+        __nv_bfloat16* dq = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2];
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          uint32_t v[32];
+          tmem_ld32(tAcc2 + lane_base + ch * 32, v);
+          tmem_ld_wait(v);
+          if (row_valid) {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(v[jj + 0]) * a.scale, __uint_as_float(v[jj + 1]) * a.scale);
+              w.y = pack_bf16(__uint_as_float(v[jj + 2]) * a.scale, __uint_as_float(v[jj + 3]) * a.scale);
+              w.z = pack_bf16(__uint_as_float(v[jj + 4]) * a.scale, __uint_as_float(v[jj + 5]) * a.scale);
+              w.w = pack_bf16(__uint_as_float(v[jj + 6]) * a.scale, __uint_as_float(v[jj + 7]) * a.scale);
+              reinterpret_cast<uint4*>(dq)[(ch * 32 + jj) >> 3] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    if (*abort_flag && lane == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// delta[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]   (fp32), HBM-bound.
+// D/8 lanes per row (16-byte loads), 32 / (D/8) rows per warp.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                                            const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                                            long long sb, long long ss, long long sh, int batch, int seq,
+                                                            int heads) {
+  constexpr int kLanes = D / 8, kRowsPerWarp = 32 / kLanes;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / kLanes, li = lane % kLanes;
+  const long long n_rows = (long long)batch * seq * heads;
+  const long long warps_total = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w * kRowsPerWarp < n_rows; w += warps_total) {
+    const long long row = w * kRowsPerWarp + sub;            // = (b * seq + s) * heads + h
+    float acc = 0.f;
+    long long b = 0, s = 0, h = 0;
+    if (row < n_rows) {
+      h = row % heads; s = (row / heads) % seq; b = row / ((long long)heads * seq);
+      const long long off = b * sb + s * ss + h * sh + li * 8;
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(o + off));
+      const uint4 y = __ldg(reinterpret_cast<const uint4*>(d_o + off));
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 xf = __bfloat1622float2(xp[t]), yf = __bfloat1622float2(yp[t]);
+        acc = fmaf(xf.x, yf.x, acc);
+        acc = fmaf(xf.y, yf.y, acc);
+      }
+    }
+#pragma unroll
+    for (int m = kLanes / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (row < n_rows && li == 0) delta[(b * heads + h) * seq + s] = acc;
+  }
+}
+
+template <int D, bool kKvOuter>
+int launch_bwd(const BwdLaunch& L, cudaStream_t stream) {
+  constexpr int smem = BwdSmem<D>::kTotal;
+  auto kern = attn_bwd_kernel<D, kKvOuter>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
+  dim3 grid(kKvOuter ? L.args.kv_heads : L.args.q_heads, L.args.list.n_outer_tiles, L.batch);
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
+}  // namespace
+
+int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream) {
+  if (L.head_dim == 128) return kv_outer ? launch_bwd<128, true>(L, stream) : launch_bwd<128, false>(L, stream);
+  if (L.head_dim == 64) return kv_outer ? launch_bwd<64, true>(L, stream) : launch_bwd<64, false>(L, stream);
+  return KVAX_B200_EUNSUPPORTED;
+}
+
+int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, const long long* strides,
+                          int batch, int seq, int heads, int head_dim, cudaStream_t stream) {
+  const long long rows = (long long)batch * seq * heads;
+  const int rows_per_warp = 32 / (head_dim / 8);
+  long long blocks = (rows / rows_per_warp + 7) / 8 + 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (head_dim == 128)
+    attn_bwd_delta_kernel<128><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, strides[0], strides[1], strides[2], batch, seq, heads);
+  else if (head_dim == 64)
+    attn_bwd_delta_kernel<64><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, strides[0], strides[1], strides[2], batch, seq, heads);
+  else
+    return KVAX_B200_EUNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
+}  // namespace kvx

@@ -38,4 +38,28 @@ struct FwdLaunch {
 };
 int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream);
 
+struct BwdArgs {
+  TileList list;            // dQ kernel: one row per query tile; dK/dV kernel: per kv tile
+  MaskView mask;            // dq mask (query-outer) or dkdv mask (kv-outer)
+  TokenInfo tok;
+  const float* lse;         // (B, Hq, Sq) base-2 log-sum-exp from the forward
+  const float* delta;       // (B, Hq, Sq) rowsum(O * dO)
+  __nv_bfloat16* dq;        // dQ kernel output, strides q_strides
+  float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) fp32 contiguous
+  float* dv;
+  int32_t* status;
+  long long q_strides[3];
+  float scale_log2e, scale;
+  int32_t q_heads, kv_heads, group;
+};
+
+struct BwdLaunch {
+  CUtensorMap tmap_x1, tmap_x2, tmap_y1, tmap_y2;
+  BwdArgs args;
+  int batch, head_dim;
+};
+int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream);
+int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, const long long* strides,
+                          int batch, int seq, int heads, int head_dim, cudaStream_t stream);
+
 }  // namespace kvx
