@@ -31,7 +31,7 @@ namespace {
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 
-enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_TFULL, B_AFULL, B_ACCFULL, B_COUNT };
+enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_TFULL, B_AFULL, B_ACCFULL, B_CFULL, B_COUNT };
 
 template <int D>
 struct BwdSmem {
@@ -45,10 +45,6 @@ struct BwdSmem {
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4 + 1024;
 };
-
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 
 template <int D, bool kKvOuter>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -96,7 +92,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   }
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(&bars[i], i == B_AFULL ? kTile : 1);
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(&bars[i], (i == B_AFULL || i == B_CFULL) ? kTile : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -219,7 +215,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
         cs[tid] = seg; cs[kTile + tid] = pos;
         cs[2 * kTile + tid] = __float_as_int(lse); cs[3 * kTile + tid] = __float_as_int(dl);
       }
-      named_barrier_sync(1, kTile);
+      mbar_arrive(&bars[B_CFULL]);          // a bounded wait instead of bar.sync: no thread can be left behind
+      ok = mbar_wait(&bars[B_CFULL], i & 1, abort_flag, a.status, B_CFULL);
+      if (!ok) break;
       ok = mbar_wait(&bars[B_TFULL], i & 1, abort_flag, a.status, B_TFULL);
       if (!ok) break;
       tc_fence_after();

@@ -1,0 +1,122 @@
+"""Backward attention kernels (delta, dQ, dK/dV) against the analytic gradients of the
+dense CPU oracle.  Tolerance of the north-star statement: max-abs 2e-2 and rel-L2 5e-3 in
+fp32 comparison, on non-PAD rows (the reference's tests zero PAD rows before comparing)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import bf16_round, compare, i32_cuda, to_bf16_cuda
+from oracle import attention_oracle as ao
+from oracle import generators as gen
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_fwd_bwd(inp, fwd_blocks=(128, 128), bwd_blocks=(128, 128), sequential=False):
+    from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status
+    from kvax_b200.ops.mask_creator import build_masks
+
+    q, k, v, do = (to_bf16_cuda(inp[n]) for n in ("q", "k", "v", "dout"))
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    bq, bk = bwd_blocks
+    masks = build_masks(p, s, p, s, [(fwd_blocks[0], fwd_blocks[1], False), (bk, bq, False), (bq, bk, True)], True)
+    out, lse, st = attention_forward(q, k, v, p, s, p, s, masks[0], fwd_blocks, inp["scale"], sequential)
+    dq, dk, dv, st2 = attention_backward(q, k, v, out, do, lse, p, s, p, s, masks[1], masks[2], bwd_blocks,
+                                         inp["scale"], sequential)
+    torch.cuda.synchronize()
+    check_status(st, "attn_fwd")
+    check_status(st2, "attn_bwd")
+    return tuple(t.float().cpu().numpy() for t in (out, dq, dk, dv))
+
+
+def _oracle_grads(inp):
+    p, s = inp["positions"], inp["segment_ids"]
+    return ao.attention_backward(bf16_round(inp["q"]), bf16_round(inp["k"]), bf16_round(inp["v"]), p, s, p, s,
+                                 inp["scale"], bf16_round(inp["dout"]), dtype=np.float64)
+
+
+def _zero_pad_dout(inp):
+    inp = dict(inp)
+    inp["dout"] = np.where((inp["segment_ids"] != -1)[:, :, None, None], inp["dout"], 0.0).astype(np.float32)
+    return inp
+
+
+def _check(inp, dq, dk, dv):
+    rq, rk, rv = _oracle_grads(inp)
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    compare("dq", dq, rq, rows)
+    compare("dk", dk, rk, rows)
+    compare("dv", dv, rv, rows)
+
+
+@pytest.mark.parametrize("head_dim", [128, 64])
+@pytest.mark.parametrize("hq,hkv", [(4, 2), (4, 4), (4, 1)])
+def test_backward_small_docmask(head_dim, hq, hkv):
+    cfg = gen.small_config(seq=1024, hq=hq, hkv=hkv, head_dim=head_dim)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=3))
+    _, dq, dk, dv = _run_fwd_bwd(inp)
+    _check(inp, dq, dk, dv)
+
+
+@pytest.mark.parametrize("bwd_blocks", [(64, 128), (64, 64), (128, 64)])
+def test_backward_mask_block_sizes(bwd_blocks):
+    cfg = gen.small_config(seq=1024, hq=2, hkv=1, head_dim=128, doc_min=40, doc_max=500)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=5, restart_positions=False))
+    _, dq, dk, dv = _run_fwd_bwd(inp, bwd_blocks=bwd_blocks)
+    _check(inp, dq, dk, dv)
+
+
+def test_backward_tiny_config_c1():
+    inp = _zero_pad_dout(gen.make_inputs(gen.CONFIGS["c1_tiny"], seed=0))
+    _, dq, dk, dv = _run_fwd_bwd(inp, fwd_blocks=(64, 64), bwd_blocks=(64, 64))
+    _check(inp, dq, dk, dv)
+
+
+def test_backward_deterministic():
+    cfg = gen.small_config(seq=2048, hq=4, hkv=1, head_dim=128)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=13))
+    a = _run_fwd_bwd(inp)
+    b = _run_fwd_bwd(inp)
+    for x, y in zip(a, b):
+        np.testing.assert_array_equal(x, y)
+
+
+def test_backward_linearity_in_dout():
+    """Size-independent property: gradients are linear in dO (checked at 8k tokens)."""
+    cfg = gen.small_config(seq=8192, batch=1, hq=4, hkv=2, head_dim=128, doc_min=128, doc_max=4096, pad=0.03)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=2))
+    _, dq1, dk1, dv1 = _run_fwd_bwd(inp)
+    inp2 = dict(inp)
+    inp2["dout"] = inp["dout"] * 2.0          # exact in bf16
+    _, dq2, dk2, dv2 = _run_fwd_bwd(inp2)
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    for a, b in ((dq1, dq2), (dk1, dk2), (dv1, dv2)):
+        a, b = np.where(rows, a, 0), np.where(rows, b, 0)
+        assert np.linalg.norm(2 * a - b) <= 4e-3 * np.linalg.norm(b)
+
+
+def test_autograd_public_api():
+    import kvax_b200 as kv
+    cfg = gen.small_config(seq=1024, hq=4, hkv=2, head_dim=128)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=21))
+    q, k, v, do = (to_bf16_cuda(inp[n]) for n in ("q", "k", "v", "dout"))
+    for t in (q, k, v):
+        t.requires_grad_(True)
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    mesh = kv.Mesh(("data", "context"), (1, 1))
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        (out.float() * do.float()).sum().backward()
+        with pytest.raises(NotImplementedError):
+            kv.flash_attention(q, k, v, p, s, p, s, masks, bias=torch.zeros(1, device="cuda"))
+        with pytest.raises(ValueError):
+            kv.flash_attention(q, k, v, p, s, p, s, (), scale=1.0)
+    assert q.grad.dtype == torch.bfloat16 and k.grad.dtype == torch.bfloat16
+    rq, rk, rv = _oracle_grads(inp)
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    # dk/dv were rounded to bf16 after the reduction: allow one bf16 ulp of the largest value
+    compare("dq", q.grad.float().cpu().numpy(), rq, rows)
+    compare("dk", k.grad.float().cpu().numpy(), rk, rows, max_abs=2e-2 + np.abs(rk).max() / 128)
+    compare("dv", v.grad.float().cpu().numpy(), rv, rows, max_abs=2e-2 + np.abs(rv).max() / 128)
