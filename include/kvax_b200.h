@@ -134,6 +134,9 @@ typedef struct kvax_b200_attn_fwd_params {
   void* out;                      /* (B, Sq, Hq, D), strides = shape.o_strides */
   float* lse;                     /* (B, Hq, Sq) */
   int32_t* status;                /* optional device int32, must be 0 on entry */
+  /* 0 = everything; else bit set: 1 tile list, 2 attention kernel (see the backward). */
+  int32_t stages;
+  int32_t reserved;
 } kvax_b200_attn_fwd_params;
 
 size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p);
@@ -157,6 +160,11 @@ typedef struct kvax_b200_attn_bwd_params {
   float* dk;                           /* (B, Skv, Hkv, D) fp32 contiguous */
   float* dv;                           /* (B, Skv, Hkv, D) fp32 contiguous */
   int32_t* status;
+  /* 0 = everything.  Otherwise a bit set of the parts to launch, for timing or profiling
+     one kernel on a workspace a full call has already filled: 1 tile lists, 2 delta,
+     4 dQ kernel, 8 dK/dV kernel. */
+  int32_t stages;
+  int32_t reserved;
 } kvax_b200_attn_bwd_params;
 
 size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p);

@@ -52,12 +52,13 @@ class AttnShape(C.Structure):
 
 class AttnFwdParams(C.Structure):
     _fields_ = [("shape", AttnShape), ("q", vp), ("k", vp), ("v", vp), ("mask", BlockMask),
-                ("out", vp), ("lse", vp), ("status", vp)]
+                ("out", vp), ("lse", vp), ("status", vp), ("stages", i32), ("reserved", i32)]
 
 
 class AttnBwdParams(C.Structure):
     _fields_ = [("shape", AttnShape), ("q", vp), ("k", vp), ("v", vp), ("out", vp), ("dout", vp), ("lse", vp),
-                ("mask_dq", BlockMask), ("mask_dkdv", BlockMask), ("dq", vp), ("dk", vp), ("dv", vp), ("status", vp)]
+                ("mask_dq", BlockMask), ("mask_dkdv", BlockMask), ("dq", vp), ("dk", vp), ("dv", vp), ("status", vp),
+                ("stages", i32), ("reserved", i32)]
 
 
 _lib = None

@@ -131,8 +131,12 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   sa.counts = reinterpret_cast<int32_t*>(ws + ll.counts_off);
   sa.n_outer_tiles = ll.n_outer; sa.n_inner_tiles = ll.n_inner;
   sa.outer_len = s.q_len; sa.inner_len = s.kv_len;
-  launch_schedule(false, sa, s.batch, st);
-  if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
+  const int stages = p->stages ? p->stages : 3;
+  if (stages & 1) {
+    launch_schedule(false, sa, s.batch, st);
+    if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
+  }
+  if (!(stages & 2)) return KVAX_B200_OK;
 
   FwdLaunch L;
   rc = make_tmap(&L.tmap_q, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);  if (rc) return rc;
@@ -194,18 +198,22 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   sq.mask = mv_dq; sq.tok = tok;
   sq.tiles = reinterpret_cast<uint32_t*>(ws + bl.dq.tiles_off); sq.counts = reinterpret_cast<int32_t*>(ws + bl.dq.counts_off);
   sq.n_outer_tiles = bl.dq.n_outer; sq.n_inner_tiles = bl.dq.n_inner; sq.outer_len = s.q_len; sq.inner_len = s.kv_len;
-  launch_schedule(false, sq, s.batch, st);
+  const int stages = p->stages ? p->stages : 15;
+  if (stages & 1) launch_schedule(false, sq, s.batch, st);
   ScheduleArgs sk;
   sk.mask = mv_dkdv; sk.tok = tok;
   sk.tiles = reinterpret_cast<uint32_t*>(ws + bl.dkdv.tiles_off); sk.counts = reinterpret_cast<int32_t*>(ws + bl.dkdv.counts_off);
   sk.n_outer_tiles = bl.dkdv.n_outer; sk.n_inner_tiles = bl.dkdv.n_inner; sk.outer_len = s.kv_len; sk.inner_len = s.q_len;
-  launch_schedule(true, sk, s.batch, st);
+  if (stages & 1) launch_schedule(true, sk, s.batch, st);
   if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
 
   long long ostr[3] = {s.o_strides[0], s.o_strides[1], s.o_strides[2]};
-  rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
-                             ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
-  if (rc) return rc;
+  if (stages & 2) {
+    rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
+                               ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
+    if (rc) return rc;
+  }
+  if (!(stages & 12)) return KVAX_B200_OK;
 
   CUtensorMap tq, tk, tv, tdo;
   rc = make_tmap(&tq, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);     if (rc) return rc;
@@ -226,8 +234,11 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   a.list.tiles = sq.tiles; a.list.counts = sq.counts; a.list.n_outer_tiles = bl.dq.n_outer; a.list.n_inner_tiles = bl.dq.n_inner;
   a.mask = mv_dq;
   L.tmap_x1 = tq; L.tmap_x2 = tdo; L.tmap_y1 = tk; L.tmap_y2 = tv;
-  rc = launch_attn_bwd(L, false, st);
-  if (rc) return rc;
+  if (stages & 4) {
+    rc = launch_attn_bwd(L, false, st);
+    if (rc) return rc;
+  }
+  if (!(stages & 8)) return KVAX_B200_OK;
   // dK/dV: resident K, V of one kv tile; streams Q, dO of every query head of the group
   a.list.tiles = sk.tiles; a.list.counts = sk.counts; a.list.n_outer_tiles = bl.dkdv.n_outer; a.list.n_inner_tiles = bl.dkdv.n_inner;
   a.mask = mv_dkdv;

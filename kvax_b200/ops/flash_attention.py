@@ -59,15 +59,16 @@ def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, sca
 
 
 def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: AttentionMask, fwd_blocks, scale,
-                      assume_sequential_positions=False, offsets=(0, 0)):
+                      assume_sequential_positions=False, offsets=(0, 0), workspace=None, stages=0, out=None, lse=None):
     """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2) with lse2 (B, Hq, Sq)
     fp32, the base-2 log-sum-exp of the scaled scores."""
     lib = _lib.load()
     B, Sq, Hq, D = q.shape
-    out = torch.empty_like(q)
-    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device) if lse is None else lse
     status = torch.zeros(1, dtype=torch.int32, device=q.device)
     p = _lib.AttnFwdParams()
+    p.stages = int(stages)
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)
@@ -76,24 +77,30 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
     if ws_bytes == 0:
         raise _lib.KvaxB200Error("kvax_b200_attn_fwd_workspace_bytes rejected the arguments "
                                  f"(head_dim={D}, dtype={q.dtype})")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if workspace is None else workspace
     with torch.cuda.device(q.device):
         rc = lib.kvax_b200_attn_fwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "kvax_b200_attn_fwd")
+    if workspace is not None or stages:
+        return out, lse, status, ws
     return out, lse, status
 
 
 def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, mask_dq: AttentionMask,
                        mask_dkdv: AttentionMask, bwd_blocks, scale, assume_sequential_positions=False,
-                       offsets=(0, 0)):
+                       offsets=(0, 0), workspace=None, stages=0, grads=None):
     """Direct wrapper of kvax_b200_attn_bwd.  Returns (dq in the input dtype, dk fp32,
     dv fp32); dk/dv are summed over the query heads of each kv head."""
     lib = _lib.load()
-    dq = torch.empty_like(q)
-    dk = torch.empty(k.shape, dtype=torch.float32, device=k.device)
-    dv = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    if grads is None:
+        dq = torch.empty_like(q)
+        dk = torch.empty(k.shape, dtype=torch.float32, device=k.device)
+        dv = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    else:
+        dq, dk, dv = grads
     status = torch.zeros(1, dtype=torch.int32, device=q.device)
     p = _lib.AttnBwdParams()
+    p.stages = int(stages)
     if out.stride() != dout.stride():
         dout = dout.contiguous()
         out = out.contiguous()
@@ -106,10 +113,12 @@ def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, ma
     ws_bytes = lib.kvax_b200_attn_bwd_workspace_bytes(p)
     if ws_bytes == 0:
         raise _lib.KvaxB200Error("kvax_b200_attn_bwd_workspace_bytes rejected the arguments")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if workspace is None else workspace
     with torch.cuda.device(q.device):
         rc = lib.kvax_b200_attn_bwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "kvax_b200_attn_bwd")
+    if workspace is not None or stages:
+        return dq, dk, dv, status, ws
     return dq, dk, dv, status
 
 

@@ -1,0 +1,79 @@
+"""Host-side logic that needs no GPU: spec registry, mesh, context-parallel offsets,
+error conventions."""
+import pytest
+import torch
+
+import kvax_b200 as kv
+from kvax_b200.ops.flash_attention import context_offsets
+from kvax_b200.utils import specs as sp
+from kvax_b200.utils.sharding import get_query_context_mesh_axis_size
+
+
+def test_specs_validation_and_restore():
+    with pytest.raises(ValueError):
+        sp.get_attention_specs()
+    with pytest.raises(ValueError):
+        sp.set_attention_specs(("d", None, None), ("d", None, None, None))
+    with pytest.raises(ValueError):
+        sp.set_attention_specs(("a", None, None, None), ("b", None, None, None))
+    with pytest.raises(ValueError):
+        sp.set_attention_specs(("a", "c", None, None), ("a", "c", None, None))       # sharded kv sequence
+    with pytest.raises(ValueError):
+        sp.set_attention_specs(("a", None, None, "m"), ("a", None, None, "m"))       # sharded head_dim
+    with kv.attention_specs(("data", "context", "model", None), ("data", None, "model", None)):
+        assert sp.get_attention_specs().query_specs[1] == "context"
+        with kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+            assert sp.get_attention_specs().query_specs[1] is None
+        assert sp.get_attention_specs().query_specs[1] == "context"
+    with pytest.raises(ValueError):
+        sp.get_attention_specs()
+
+
+def test_mesh_coordinates_and_axis_lookup():
+    m = kv.Mesh(("data", "context", "model"), (2, 4, 2), rank=13)   # 13 = (1*4 + 2)*2 + 1
+    assert (m.coordinate("data"), m.coordinate("context"), m.coordinate("model")) == (1, 2, 1)
+    with kv.attention_specs(("data", "context", "model", None), ("data", None, "model", None)):
+        assert get_query_context_mesh_axis_size(m) == 4
+        with m:
+            assert get_query_context_mesh_axis_size(None) == 4
+        with pytest.raises(ValueError):
+            get_query_context_mesh_axis_size(None)                   # no mesh in scope
+    with kv.attention_specs(("data", "ctx", None, None), ("data", None, None, None)):
+        with pytest.raises(ValueError):
+            get_query_context_mesh_axis_size(m)                      # axis not in the mesh
+
+
+def test_context_offsets_give_global_indices():
+    """offset + local index must equal the global index of the token, for both halves
+    (rank r holds chunk r then chunk 2CP-1-r of the permuted sequence)."""
+    for cp in (2, 4, 8):
+        S = 1024 * cp
+        loc = S // cp
+        half = loc // 2
+        for r in range(cp):
+            first, second = context_offsets(r, cp, loc, permuted=True)
+            assert first + 0 == r * half
+            assert second + half == (2 * cp - 1 - r) * half
+            f2, s2 = context_offsets(r, cp, loc, permuted=False)
+            assert f2 == s2 == r * loc
+    assert context_offsets(0, 1, 512, True) == (0, 0)
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    x = torch.zeros(2, 16, dtype=torch.int32)
+    m = kv.Mesh(("data", "context"), (1, 2), rank=0)
+    with m, kv.attention_specs(("data", "context", None, None), ("data", None, None, None)):
+        with pytest.raises(RuntimeError):
+            kv.permute_tokens_context_parallelism(x)
+        with pytest.raises(RuntimeError):
+            kv.create_attention_mask(x, x, x, x, fwd_params=kv.FlashAttentionParamsConfig(8, 8))
+
+
+def test_flop_formula():
+    from kvax_b200.utils.math import get_multi_head_attention_tflops as f
+    base = f(2, 1024, 1024, 8, 128, 128, causal=False)
+    assert base == pytest.approx(2 * 8 * 2 * 256 * 1024 * 1024 / 1e12)
+    assert f(2, 1024, 1024, 8, 128, 128, causal=True, backward_pass=True) == pytest.approx(base * 0.5 * 3.5)
+    assert f(2, 1024, 1024, 8, 128, 128, causal=False, forward_pass=False, backward_pass=True) == pytest.approx(base * 2.5)
+    with pytest.raises(ValueError):
+        f(1, 1, 1, 1, 1, 1, causal=False, forward_pass=False, backward_pass=False)
