@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <string.h>
+#include <stdlib.h>
 
 #include "../../include/kvax_b200.h"
 #include "internal.h"
@@ -77,15 +78,42 @@ int mask_view(const kvax_b200_block_mask& m, bool kv_outer, int q_len, int kv_le
   return KVAX_B200_OK;
 }
 
-struct ListLayout { size_t tiles_off, counts_off, total; int n_outer, n_inner; };
+struct ListLayout { size_t tiles_off, counts_off, order_off, total; int n_outer, n_inner; };
 
 ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base) {
   ListLayout l;
   l.n_outer = cdiv(outer_len, kTile); l.n_inner = cdiv(inner_len, kTile);
   l.tiles_off = base;
   l.counts_off = l.tiles_off + align256(size_t(batch) * l.n_outer * l.n_inner * sizeof(uint32_t));
-  l.total = l.counts_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
+  l.order_off = l.counts_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
+  l.total = l.order_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
   return l;
+}
+
+// per-tile summaries of both sides: query tiles first, kv tiles after
+struct SummaryLayout { size_t q_off, kv_off, total; };
+SummaryLayout summary_layout(int batch, int q_len, int kv_len, size_t base) {
+  SummaryLayout l;
+  l.q_off = base;
+  l.kv_off = l.q_off + align256(size_t(batch) * cdiv(q_len, kTile) * sizeof(int4));
+  l.total = l.kv_off + align256(size_t(batch) * cdiv(kv_len, kTile) * sizeof(int4));
+  return l;
+}
+
+void fill_schedule(ScheduleArgs* sa, const MaskView& mv, const TokenInfo& tok, char* ws, const ListLayout& ll,
+                   const int4* inner_summary, int outer_len, int inner_len) {
+  sa->mask = mv; sa->tok = tok;
+  sa->tiles = reinterpret_cast<uint32_t*>(ws + ll.tiles_off);
+  sa->counts = reinterpret_cast<int32_t*>(ws + ll.counts_off);
+  sa->order = reinterpret_cast<int32_t*>(ws + ll.order_off);
+  sa->inner_summary = inner_summary;
+  sa->n_outer_tiles = ll.n_outer; sa->n_inner_tiles = ll.n_inner;
+  sa->outer_len = outer_len; sa->inner_len = inner_len;
+}
+
+void fill_list(TileList* l, const ScheduleArgs& sa) {
+  l->tiles = sa.tiles; l->counts = sa.counts; l->order = sa.order;
+  l->n_outer_tiles = sa.n_outer_tiles; l->n_inner_tiles = sa.n_inner_tiles;
 }
 
 }  // namespace
@@ -106,7 +134,8 @@ extern "C" const char* kvax_b200_error_string(int code) {
 
 extern "C" size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p) {
   if (!p || check_shape(p->shape) != KVAX_B200_OK) return 0;
-  return list_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, 0).total;
+  const ListLayout ll = list_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, 0);
+  return summary_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, ll.total).total;
 }
 
 extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,
@@ -116,7 +145,8 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   int rc = check_shape(s);
   if (rc) return rc;
   const ListLayout ll = list_layout(s.batch, s.q_len, s.kv_len, 0);
-  if (!workspace || workspace_bytes < ll.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
+  const SummaryLayout sl = summary_layout(s.batch, s.q_len, s.kv_len, ll.total);
+  if (!workspace || workspace_bytes < sl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
   if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2]) & 7 || (reinterpret_cast<uintptr_t>(p->out) & 15)) return KVAX_B200_EUNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
@@ -126,13 +156,12 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   if (rc) return rc;
 
   ScheduleArgs sa;
-  sa.mask = mv; sa.tok = token_info(s);
-  sa.tiles = reinterpret_cast<uint32_t*>(ws + ll.tiles_off);
-  sa.counts = reinterpret_cast<int32_t*>(ws + ll.counts_off);
-  sa.n_outer_tiles = ll.n_outer; sa.n_inner_tiles = ll.n_inner;
-  sa.outer_len = s.q_len; sa.inner_len = s.kv_len;
+  int4* q_sum = reinterpret_cast<int4*>(ws + sl.q_off);
+  int4* kv_sum = reinterpret_cast<int4*>(ws + sl.kv_off);
+  fill_schedule(&sa, mv, token_info(s), ws, ll, kv_sum, s.q_len, s.kv_len);
   const int stages = p->stages ? p->stages : 3;
   if (stages & 1) {
+    launch_tile_summaries(sa.tok, s.batch, q_sum, kv_sum, st);
     launch_schedule(false, sa, s.batch, st);
     if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
   }
@@ -143,26 +172,26 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   rc = make_tmap(&L.tmap_k, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides); if (rc) return rc;
   rc = make_tmap(&L.tmap_v, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides); if (rc) return rc;
   FwdArgs& a = L.args;
-  a.list.tiles = sa.tiles; a.list.counts = sa.counts;
-  a.list.n_outer_tiles = ll.n_outer; a.list.n_inner_tiles = ll.n_inner;
+  fill_list(&a.list, sa);
   a.mask = mv; a.tok = sa.tok;
   a.out = static_cast<__nv_bfloat16*>(p->out); a.lse = p->lse; a.status = p->status;
   for (int i = 0; i < 3; ++i) a.o_strides[i] = s.o_strides[i];
   a.scale_log2e = s.scale * 1.4426950408889634f;
-  a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads;
+  a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;
   return launch_attn_fwd(L, st);
 }
 
 namespace {
 
-struct BwdLayout { ListLayout dq, dkdv; size_t delta_off, total; };
+struct BwdLayout { ListLayout dq, dkdv; SummaryLayout sum; size_t delta_off, total; };
 
 BwdLayout bwd_layout(const kvax_b200_attn_shape& s) {
   BwdLayout l;
   l.dq = list_layout(s.batch, s.q_len, s.kv_len, 0);
   l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total);
-  l.delta_off = l.dkdv.total;
+  l.sum = summary_layout(s.batch, s.q_len, s.kv_len, l.dkdv.total);
+  l.delta_off = l.sum.total;
   l.total = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));
   return l;
 }
@@ -194,17 +223,17 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   rc = mask_view(p->mask_dq, false, s.q_len, s.kv_len, &mv_dq);     if (rc) return rc;
   rc = mask_view(p->mask_dkdv, true, s.q_len, s.kv_len, &mv_dkdv);  if (rc) return rc;
 
-  ScheduleArgs sq;
-  sq.mask = mv_dq; sq.tok = tok;
-  sq.tiles = reinterpret_cast<uint32_t*>(ws + bl.dq.tiles_off); sq.counts = reinterpret_cast<int32_t*>(ws + bl.dq.counts_off);
-  sq.n_outer_tiles = bl.dq.n_outer; sq.n_inner_tiles = bl.dq.n_inner; sq.outer_len = s.q_len; sq.inner_len = s.kv_len;
+  int4* q_sum = reinterpret_cast<int4*>(ws + bl.sum.q_off);
+  int4* kv_sum = reinterpret_cast<int4*>(ws + bl.sum.kv_off);
+  ScheduleArgs sq, sk;
+  fill_schedule(&sq, mv_dq, tok, ws, bl.dq, kv_sum, s.q_len, s.kv_len);
+  fill_schedule(&sk, mv_dkdv, tok, ws, bl.dkdv, q_sum, s.kv_len, s.q_len);
   const int stages = p->stages ? p->stages : 15;
-  if (stages & 1) launch_schedule(false, sq, s.batch, st);
-  ScheduleArgs sk;
-  sk.mask = mv_dkdv; sk.tok = tok;
-  sk.tiles = reinterpret_cast<uint32_t*>(ws + bl.dkdv.tiles_off); sk.counts = reinterpret_cast<int32_t*>(ws + bl.dkdv.counts_off);
-  sk.n_outer_tiles = bl.dkdv.n_outer; sk.n_inner_tiles = bl.dkdv.n_inner; sk.outer_len = s.kv_len; sk.inner_len = s.q_len;
-  if (stages & 1) launch_schedule(true, sk, s.batch, st);
+  if (stages & 1) {
+    launch_tile_summaries(tok, s.batch, q_sum, kv_sum, st);
+    launch_schedule(false, sq, s.batch, st);
+    launch_schedule(true, sk, s.batch, st);
+  }
   if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
 
   long long ostr[3] = {s.o_strides[0], s.o_strides[1], s.o_strides[2]};
@@ -228,10 +257,12 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   for (int i = 0; i < 3; ++i) a.q_strides[i] = s.q_strides[i];
   a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;
+  { const char* e = getenv("KVAX_B200_DEBUG"); a.debug = e ? atoi(e) : 0; }
+  a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;
 
   // dQ: resident Q, dO of one query tile; streams K, V
-  a.list.tiles = sq.tiles; a.list.counts = sq.counts; a.list.n_outer_tiles = bl.dq.n_outer; a.list.n_inner_tiles = bl.dq.n_inner;
+  fill_list(&a.list, sq);
   a.mask = mv_dq;
   L.tmap_x1 = tq; L.tmap_x2 = tdo; L.tmap_y1 = tk; L.tmap_y2 = tv;
   if (stages & 4) {
@@ -240,7 +271,7 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   }
   if (!(stages & 8)) return KVAX_B200_OK;
   // dK/dV: resident K, V of one kv tile; streams Q, dO of every query head of the group
-  a.list.tiles = sk.tiles; a.list.counts = sk.counts; a.list.n_outer_tiles = bl.dkdv.n_outer; a.list.n_inner_tiles = bl.dkdv.n_inner;
+  fill_list(&a.list, sk);
   a.mask = mv_dkdv;
   L.tmap_x1 = tk; L.tmap_x2 = tv; L.tmap_y1 = tq; L.tmap_y2 = tdo;
   return launch_attn_bwd(L, true, st);

@@ -13,7 +13,12 @@
 //     ACC1 += P  * Y2   (dV += P^T dO;  dK/dV kernel only)  tcgen05, A from TMEM
 //     ACC2 += dS * Y1   (dQ += dS K  or  dK += dS^T Q)      tcgen05, A from TMEM
 // Warps 0-3 do the register math (thread t = outer row t = TMEM lane t), warp 4 is the
-// TMA producer, warp 5 issues the MMAs.  The query heads of a GQA group are accumulated
+// TMA producer, warp 5 issues the MMAs.  The MMA order is software-pipelined so that the
+// tensor pipe always has work while the register math of the neighbouring step runs:
+//     ... | ACC1(i), T1(i+1) | ACC2(i), T2(i+1) | ACC1(i+1), T1(i+2) | ...
+// T1(i+1) may overwrite the P(i) columns because tcgen05.mma instructions of one thread
+// execute in issue order and ACC1(i) (the reader of P(i)) is issued first; likewise
+// T2(i+1) after ACC2(i).  The query heads of a GQA group are accumulated
 // on chip by the dK/dV kernel, so dK/dV leave the kernel already summed over the group
 // (the reference sums a (B, Hq, Skv, D) fp32 temporary afterwards,
 // kvax/ops/flash_attention_triton.py:1855-1868).
@@ -28,10 +33,14 @@ namespace kvx {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kComputeWarps = 8;                    // two per SM sub-partition
+constexpr int kComputeThreads = kComputeWarps * 32;
+constexpr int kProducerWarp = kComputeWarps, kMmaWarp = kComputeWarps + 1;
+constexpr int kThreads = (kComputeWarps + 2) * 32;
 constexpr int kTmemCols = 512;
+constexpr int kHalf = kTile / 2;                    // columns handled by one compute thread
 
-enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_TFULL, B_AFULL, B_ACCFULL, B_CFULL, B_COUNT };
+enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_SFULL, B_DPFULL, B_PFULL, B_DSFULL, B_ACCFULL, B_CFULL, B_COUNT };
 
 template <int D>
 struct BwdSmem {
@@ -46,6 +55,10 @@ struct BwdSmem {
   static constexpr int kTotal = kAbort + 4 + 1024;
 };
 
+// Compute thread layout: thread t of the 256 owns outer row (t % 128) = TMEM lane, and the
+// column half (t / 128) of every 128-column tile.  P and dS (bf16 pairs) of half h are
+// written back at column offset 64*h of the T1 / T2 regions, i.e. inside the fp32 columns
+// that same thread has already read, so the two halves never touch each other's columns.
 template <int D, bool kKvOuter>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_constant__ CUtensorMap tmap_x2,
@@ -60,43 +73,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   int* s_cols = reinterpret_cast<int*>(smem + L::kCols);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int xh = blockIdx.x;                 // dQ: query head; dK/dV: kv head
-  const int ot = blockIdx.y, b = blockIdx.z; // outer tile, batch
+  int row_rank, xh;                          // xh: query head (dQ kernel) or kv head (dK/dV kernel)
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, kKvOuter ? a.kv_heads : a.q_heads, &row_rank, &xh);
+  const long long list_row = __ldg(a.list.order + row_rank);     // longest lists first
+  const int b = int(list_row / a.list.n_outer_tiles), ot = int(list_row % a.list.n_outer_tiles);
   const int group = a.group;
-  const long long list_row = (long long)b * a.list.n_outer_tiles + ot;
   const int count = __ldg(a.list.counts + list_row);
   const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
   const int n_items = kKvOuter ? count * group : count;
   const int outer_len = kKvOuter ? a.tok.kv_len : a.tok.q_len;
   const int inner_len = kKvOuter ? a.tok.q_len : a.tok.kv_len;
 
-  const int r = ot * kTile + tid;            // outer row of a compute thread
-  const bool row_valid = (tid < kTile) && (r < outer_len);
+  const int row = tid & (kTile - 1);         // outer row / TMEM lane of a compute thread
+  const int half = (tid >> 7) & 1;           // column half of a compute thread
+  const int r = ot * kTile + row;
+  const bool is_compute = tid < kComputeThreads;
+  const bool row_valid = is_compute && (r < outer_len);
 
   if (n_items == 0) {                        // no contributing tile: zero gradients
     if (row_valid) {
       if (kKvOuter) {
         float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4* dk = reinterpret_cast<float4*>(a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D);
-        float4* dv = reinterpret_cast<float4*>(a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D);
+        float4* dk = reinterpret_cast<float4*>(a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D) + half * (D / 8);
+        float4* dv = reinterpret_cast<float4*>(a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D) + half * (D / 8);
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) { dk[i] = z; dv[i] = z; }
+        for (int i = 0; i < D / 8; ++i) { dk[i] = z; dv[i] = z; }
       } else {
         uint4 z = make_uint4(0, 0, 0, 0);
-        uint4* dq = reinterpret_cast<uint4*>(a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2]);
+        uint4* dq = reinterpret_cast<uint4*>(a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2]) + half * (D / 16);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) dq[i] = z;
+        for (int i = 0; i < D / 16; ++i) dq[i] = z;
       }
     }
     return;
   }
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(&bars[i], (i == B_AFULL || i == B_CFULL) ? kTile : 1);
+    for (int i = 0; i < B_COUNT; ++i)
+      mbar_init(&bars[i], (i == B_PFULL || i == B_DSFULL || i == B_CFULL) ? kComputeThreads : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == kProducerWarp) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -104,7 +122,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   const uint32_t tT1 = tmem_base, tT2 = tmem_base + kTile;
   const uint32_t tAcc1 = tmem_base + 2 * kTile, tAcc2 = tmem_base + 3 * kTile;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       prefetch_tmap(&tmap_x1); prefetch_tmap(&tmap_x2); prefetch_tmap(&tmap_y1); prefetch_tmap(&tmap_y2);
@@ -132,51 +150,75 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
       const uint32_t x1 = smem_u32(smem + L::kX1), x2 = smem_u32(smem + L::kX2);
+      const uint32_t ybase = smem_u32(smem + L::kY);
+      auto issue_t = [&](uint32_t t_addr, uint32_t x, uint32_t y) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
+          umma_ss(t_addr, make_sdesc_sw128(x + off, 16, 1024), make_sdesc_sw128(y + off, 16, 1024), idesc_t, kk > 0);
+        }
+      };
+      // A operand (bf16 pairs in TMEM): K-steps 0-3 at column offset 0, K-steps 4-7 at offset 64
+      auto issue_acc = [&](uint32_t acc_addr, uint32_t a_addr, uint32_t y, uint32_t acc_on) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(acc_addr, a_addr + (kk >> 2) * kHalf + (kk & 3) * 8, make_sdesc_sw128(y + kk * 16 * 128, L::kBoxBytes, 1024),
+                  idesc_acc, acc_on | (kk > 0));
+      };
       bool ok = mbar_wait(&bars[B_XFULL], 0, abort_flag, a.status, B_XFULL);
+      if (ok) ok = mbar_wait(&bars[B_YFULL0], 0, abort_flag, a.status, B_YFULL0);
+      if (ok) {
+        tc_fence_after();
+        issue_t(tT1, x1, ybase);
+        umma_commit(&bars[B_SFULL]);
+        issue_t(tT2, x2, ybase + L::kTileBytes);
+        umma_commit(&bars[B_DPFULL]);
+      }
       for (int i = 0; i < n_items && ok; ++i) {
         const int st = i & 1;
-        const uint32_t y1 = smem_u32(smem + L::kY + st * 2 * L::kTileBytes), y2 = y1 + L::kTileBytes;
-        ok = mbar_wait(&bars[B_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_YFULL0 + st);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
-          umma_ss(tT1, make_sdesc_sw128(x1 + off, 16, 1024), make_sdesc_sw128(y1 + off, 16, 1024), idesc_t, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
-          umma_ss(tT2, make_sdesc_sw128(x2 + off, 16, 1024), make_sdesc_sw128(y2 + off, 16, 1024), idesc_t, kk > 0);
-        }
-        umma_commit(&bars[B_TFULL]);
-        ok = mbar_wait(&bars[B_AFULL], i & 1, abort_flag, a.status, B_AFULL);
-        if (!ok) break;
-        tc_fence_after();
+        const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
+        const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
         const uint32_t acc_on = (i > 0) ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          if (kKvOuter)
-            umma_ts(tAcc1, tT1 + kk * 8, make_sdesc_sw128(y2 + kk * 16 * 128, L::kBoxBytes, 1024), idesc_acc, acc_on | (kk > 0));
-          umma_ts(tAcc2, tT2 + kk * 8, make_sdesc_sw128(y1 + kk * 16 * 128, L::kBoxBytes, 1024), idesc_acc, acc_on | (kk > 0));
+        const bool more = (i + 1 < n_items);
+        ok = mbar_wait(&bars[B_PFULL], i & 1, abort_flag, a.status, B_PFULL);     // P(i) written, S(i) consumed
+        if (!ok) break;
+        tc_fence_after();
+        if (kKvOuter) issue_acc(tAcc1, tT1, y2, acc_on);                            // dV += P^T dO
+        if (more) {
+          ok = mbar_wait(&bars[B_YFULL0 + (st ^ 1)], ((i + 1) >> 1) & 1, abort_flag, a.status, B_YFULL0 + (st ^ 1));
+          if (!ok) break;
+          tc_fence_after();
+          issue_t(tT1, x1, y1n);                                                    // scores of item i+1
+          umma_commit(&bars[B_SFULL]);
         }
+        ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(tAcc2, tT2, y1, acc_on);                                          // dQ += dS K  /  dK += dS^T Q
         umma_commit(&bars[B_YEMPTY0 + st]);
-        if (i == n_items - 1) umma_commit(&bars[B_ACCFULL]);
+        if (more) {
+          issue_t(tT2, x2, y2n);                                                    // dP of item i+1
+          umma_commit(&bars[B_DPFULL]);
+        } else {
+          umma_commit(&bars[B_ACCFULL]);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------------ register math
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t my_t1 = tT1 + lane_base + half * kHalf;      // fp32 columns of this thread; P goes to the first 32 of them
+    const uint32_t my_t2 = tT2 + lane_base + half * kHalf;
     const float c = a.scale_log2e;
     const RowBounds rb = load_bounds(a.mask, b, min(r, outer_len - 1));
     int o_seg = KVAX_B200_PADDING_SEGMENT_ID, o_pos = 0;
-    float row_lse = 0.f, row_delta = 0.f;
+    float row_neg_lse = 0.f, row_delta = 0.f;
     if (row_valid) {
       if (kKvOuter) {
         o_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
@@ -184,7 +226,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       } else {
         o_seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + r);
         o_pos = query_position(a.tok, b, r);
-        row_lse = __ldg(a.lse + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
+        row_neg_lse = -__ldg(a.lse + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
         row_delta = __ldg(a.delta + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
       }
     }
@@ -194,88 +236,130 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       const uint32_t e = __ldg(list + j);
       const int c0 = int(e & ~kPartialBit) * kTile;
       const bool partial = (e & kPartialBit) != 0;
-      // per-column info of this inner tile: segment id, position (partial tiles only) and,
-      // for the dK/dV kernel, LSE2 and delta of the query rows
+      // per-column info of this inner tile (one column per thread of the first half):
+      // segment id and position (partial tiles only) and, for the dK/dV kernel, -LSE2 and
+      // delta of the query rows
       int* cs = s_cols + (i & 1) * 4 * kTile;
-      {
-        const int col = c0 + tid;
+      if ((kKvOuter || partial) && half == 0) {
+        const int col = c0 + row;
         int seg = KVAX_B200_PADDING_SEGMENT_ID, pos = 0;
-        float lse = INFINITY, dl = 0.f;
+        float nlse = -INFINITY, dl = 0.f;
         if (col < inner_len) {
           if (kKvOuter) {
             const int yh = xh * group + i / count;
             const long long o = ((long long)b * a.q_heads + yh) * a.tok.q_len + col;
-            lse = __ldg(a.lse + o); dl = __ldg(a.delta + o);
+            nlse = -__ldg(a.lse + o); dl = __ldg(a.delta + o);
             if (partial) { seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + col); pos = query_position(a.tok, b, col); }
-          } else if (partial) {
+          } else {
             seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + col);
             pos = a.tok.sequential ? col : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + col);
           }
         }
-        cs[tid] = seg; cs[kTile + tid] = pos;
-        cs[2 * kTile + tid] = __float_as_int(lse); cs[3 * kTile + tid] = __float_as_int(dl);
+        cs[row] = seg; cs[kTile + row] = pos;
+        cs[2 * kTile + row] = __float_as_int(nlse); cs[3 * kTile + row] = __float_as_int(dl);
       }
       mbar_arrive(&bars[B_CFULL]);          // a bounded wait instead of bar.sync: no thread can be left behind
       ok = mbar_wait(&bars[B_CFULL], i & 1, abort_flag, a.status, B_CFULL);
       if (!ok) break;
-      ok = mbar_wait(&bars[B_TFULL], i & 1, abort_flag, a.status, B_TFULL);
-      if (!ok) break;
-      tc_fence_after();
+      const int cb = half * kHalf;            // first column (within the tile) of this thread
+      const float4* cs_nlse = reinterpret_cast<const float4*>(cs + 2 * kTile + cb);
+      const float4* cs_dl = reinterpret_cast<const float4*>(cs + 3 * kTile + cb);
+
+      // element mask of partial tiles, one bit per column of this thread's half
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
+      if (partial) {
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tT1 + lane_base + ch * 32, s);
-        tmem_ld32(tT2 + lane_base + ch * 32, dp);
-        uint32_t keep = 0xffffffffu;
-        if (partial) {
-          keep = 0;
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t bits = 0;
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) {
-            const int ci = ch * 32 + jj, col = c0 + ci;
+            const int ci = cb + ch * 32 + jj, col = c0 + ci;
             const bool seg_eq = (cs[ci] == o_seg);
             const bool causal = kKvOuter ? (cs[kTile + ci] >= o_pos) : (o_pos >= cs[kTile + ci]);
             const bool al = row_valid && (col < inner_len) && element_allowed<kKvOuter>(rb, col, seg_eq, causal);
-            keep |= (al ? 1u : 0u) << jj;
+            bits |= (al ? 1u : 0u) << jj;
+          }
+          keep[ch] = bits;
+        }
+      }
+
+      // ---- P = exp2(S * scale*log2e - LSE2): the 64 values of this thread stay in registers
+      ok = mbar_wait(&bars[B_SFULL], i & 1, abort_flag, a.status, B_SFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[2][32];
+      tmem_ld32(my_t1, v[0]);
+      tmem_ld32(my_t1 + 32, v[1]);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        tmem_ld_wait(v[ch]);
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 4) {
+          float4 nl = make_float4(row_neg_lse, row_neg_lse, row_neg_lse, row_neg_lse);
+          if (kKvOuter) nl = cs_nlse[(ch * 32 + jj) >> 2];
+          const float n4[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj + t]), c, n4[t]));
+            if (partial) pv = ((keep[ch] >> (jj + t)) & 1u) ? pv : 0.f;
+            v[ch][jj + t] = __float_as_uint(pv);
           }
         }
-        tmem_ld_wait(s);
-        tmem_ld_wait(dp);
-        uint32_t pk[16], dk[16];
+        if (kKvOuter) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          float p[2], ds[2];
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const int ci = ch * 32 + jj + t;
-            const float lse = kKvOuter ? __int_as_float(cs[2 * kTile + ci]) : row_lse;
-            const float dl = kKvOuter ? __int_as_float(cs[3 * kTile + ci]) : row_delta;
-            float pv = fast_exp2(fmaf(__uint_as_float(s[jj + t]), c, -lse));
-            pv = ((keep >> (jj + t)) & 1u) ? pv : 0.f;
-            p[t] = pv;
-            ds[t] = pv * (__uint_as_float(dp[jj + t]) - dl);
-          }
-          pk[jj >> 1] = pack_bf16(p[0], p[1]);
-          dk[jj >> 1] = pack_bf16(ds[0], ds[1]);
+          for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
+          tmem_st16(my_t1 + ch * 16, pk);
         }
-        if (kKvOuter) tmem_st16(tT1 + lane_base + ch * 16, pk);
-        tmem_st16(tT2 + lane_base + ch * 16, dk);
+      }
+      if (kKvOuter) tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[B_PFULL]);
+
+      // ---- dS = P * (dP - delta)
+      ok = mbar_wait(&bars[B_DPFULL], i & 1, abort_flag, a.status, B_DPFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dp[2][32];
+      tmem_ld32(my_t2, dp[0]);
+      tmem_ld32(my_t2 + 32, dp[1]);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        tmem_ld_wait(dp[ch]);
+        uint32_t dk[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 4) {
+          float4 dl = make_float4(row_delta, row_delta, row_delta, row_delta);
+          if (kKvOuter) dl = cs_dl[(ch * 32 + jj) >> 2];
+          const float d0 = __uint_as_float(v[ch][jj + 0]) * (__uint_as_float(dp[ch][jj + 0]) - dl.x);
+          const float d1 = __uint_as_float(v[ch][jj + 1]) * (__uint_as_float(dp[ch][jj + 1]) - dl.y);
+          const float d2 = __uint_as_float(v[ch][jj + 2]) * (__uint_as_float(dp[ch][jj + 2]) - dl.z);
+          const float d3 = __uint_as_float(v[ch][jj + 3]) * (__uint_as_float(dp[ch][jj + 3]) - dl.w);
+          dk[jj >> 1] = pack_bf16(d0, d1);
+          dk[(jj >> 1) + 1] = pack_bf16(d2, d3);
+        }
+        // both 32-column chunks were loaded before the first store, so writing over the
+        // first 32 columns is safe
+        tmem_st16(my_t2 + ch * 16, dk);
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars[B_AFULL]);
+      mbar_arrive(&bars[B_DSFULL]);
     }
 
     if (ok) ok = mbar_wait(&bars[B_ACCFULL], 0, abort_flag, a.status, B_ACCFULL);
     if (ok) {
       tc_fence_after();
+      // each thread stores D/2 columns of its row: columns [half*D/2, (half+1)*D/2)
+      constexpr int kCh = D / 64;             // 32-column chunks per thread
       if (kKvOuter) {
-        float* dk = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D;
-        float* dv = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D;
+        float* dk = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D + half * (D / 2);
+        float* dv = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D + half * (D / 2);
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ch = 0; ch < kCh; ++ch) {
           uint32_t v1[32], v2[32];
-          tmem_ld32(tAcc1 + lane_base + ch * 32, v1);
-          tmem_ld32(tAcc2 + lane_base + ch * 32, v2);
+          tmem_ld32(tAcc1 + lane_base + half * (D / 2) + ch * 32, v1);
+          tmem_ld32(tAcc2 + lane_base + half * (D / 2) + ch * 32, v2);
           tmem_ld_wait(v1);
           tmem_ld_wait(v2);
           if (row_valid) {
@@ -290,11 +374,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
           }
         }
       } else {
-        __nv_bfloat16* dq = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2];
+        __nv_bfloat16* dq = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2] + half * (D / 2);
 #pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
+        for (int ch = 0; ch < kCh; ++ch) {
           uint32_t v[32];
-          tmem_ld32(tAcc2 + lane_base + ch * 32, v);
+          tmem_ld32(tAcc2 + lane_base + half * (D / 2) + ch * 32, v);
           tmem_ld_wait(v);
           if (row_valid) {
 #pragma unroll
@@ -314,7 +398,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (*abort_flag && lane == 0) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) { }
@@ -365,7 +449,7 @@ int launch_bwd(const BwdLaunch& L, cudaStream_t stream) {
   constexpr int smem = BwdSmem<D>::kTotal;
   auto kern = attn_bwd_kernel<D, kKvOuter>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
-  dim3 grid(kKvOuter ? L.args.kv_heads : L.args.q_heads, L.args.list.n_outer_tiles, L.batch);
+  dim3 grid(L.args.list.n_outer_tiles * L.batch * (kKvOuter ? L.args.kv_heads : L.args.q_heads), 1, 1);
   kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }

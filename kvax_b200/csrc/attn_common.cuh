@@ -77,7 +77,23 @@ __device__ __forceinline__ bool element_allowed(const RowBounds& rb, int i, bool
 struct TileList {
   const uint32_t* tiles;   // (B, n_outer_tiles, n_inner_tiles)
   const int32_t* counts;   // (B, n_outer_tiles)
+  const int32_t* order;    // (B * n_outer_tiles) launch order: row = b * n_outer_tiles + tile
   int32_t n_outer_tiles, n_inner_tiles;
 };
+
+// Launch geometry shared by the attention kernels: a 1-D grid over (outer tile, head).
+// Outer tiles are taken in the longest-first order, in chunks of kRowChunk; inside a chunk
+// the heads are the slow index.  CTAs resident at the same time therefore belong to a few
+// heads and neighbouring outer tiles, so they stream the same inner tiles (served by L2),
+// while long work items still start early in the launch.
+constexpr int kRowChunk = 32;
+__device__ __forceinline__ void decode_block(int linear, int n_rows, int n_heads, int* row_rank, int* head) {
+  const int per_chunk = kRowChunk * n_heads;
+  const int chunk = linear / per_chunk;
+  const int within = linear - chunk * per_chunk;
+  const int rows_here = min(kRowChunk, n_rows - chunk * kRowChunk);
+  *head = within / rows_here;
+  *row_rank = chunk * kRowChunk + (within - *head * rows_here);
+}
 
 }  // namespace kvx

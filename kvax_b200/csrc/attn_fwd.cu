@@ -59,9 +59,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbort);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.x, qt = blockIdx.y, b = blockIdx.z;
+  int row_rank, h;
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.q_heads, &row_rank, &h);
+  const long long list_row = __ldg(a.list.order + row_rank);       // longest lists first
+  const int b = int(list_row / a.list.n_outer_tiles), qt = int(list_row % a.list.n_outer_tiles);
   const int kvh = h / a.group;
-  const long long list_row = (long long)b * a.list.n_outer_tiles + qt;
   const int count = __ldg(a.list.counts + list_row);
   const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
 
@@ -161,24 +163,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int32_t* kv_seg = a.tok.kv_seg + (long long)b * a.tok.kv_len;
     const int32_t* kv_pos = a.tok.kv_pos + (long long)b * a.tok.kv_len;
 
+    // Online softmax state.  `m` is the reference maximum the exponentials use.  It only
+    // follows the true running maximum when that has grown by more than kLazy (log2
+    // units): P then stays below 2^kLazy, and the accumulator in TMEM needs no rescaling
+    // for small increases.  O / l and LSE2 = m + log2(l) do not depend on the choice.
+    constexpr float kLazy = 8.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int it = 0; it < count && ok; ++it) {
       const uint32_t e = __ldg(list + it);
       const int c0 = int(e & ~kPartialBit) * kTile;
       const bool partial = (e & kPartialBit) != 0;
-      ok = mbar_wait(&bars[B_SFULL], it & 1, abort_flag, a.status, B_SFULL);
-      if (!ok) break;
-      tc_fence_after();
 
-      // pass 1: row maximum (and, on partial tiles, the per-element keep bits)
+      // element mask of partial tiles (computed before the scores arrive)
       uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      float mx = -INFINITY;
+      if (partial) {
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(tS + lane_base + ch * 32, v);
-        if (partial) {
+        for (int ch = 0; ch < 4; ++ch) {
           uint32_t bits = 0;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -193,16 +194,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
           keep[ch] = bits;
         }
-        tmem_ld_wait(v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float s = __uint_as_float(v[j]) * c;
-          mx = fmaxf(mx, ((keep[ch] >> j) & 1u) ? s : -INFINITY);
-        }
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_safe);          // 0 when m was -inf
+
+      ok = mbar_wait(&bars[B_SFULL], it & 1, abort_flag, a.status, B_SFULL);
+      if (!ok) break;
+      tc_fence_after();
+
+      // pass 1: row maximum of the raw scores (scaled afterwards: scale > 0)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tS + lane_base + ch * 32, v);
+        tmem_ld_wait(v);
+        if (partial) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = ((keep[ch] >> j) & 1u) ? v[j] : 0xff800000u;   // -inf
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) mx = fmax3(mx, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+      }
+      mx *= c;
+      float alpha = 1.f;
+      if (mx - m > kLazy) {                     // also taken when m is still -inf
+        alpha = fast_exp2(m - mx);              // 0 when m was -inf
+        m = mx;
+      }
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
 
       // pass 2: p = exp2(s*c - m), row sum, P (bf16 pairs) back into the score columns
       float rowsum = 0.f;
@@ -214,19 +232,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(v[j]), c, -m_safe));
-          float p1 = fast_exp2(fmaf(__uint_as_float(v[j + 1]), c, -m_safe));
-          p0 = ((keep[ch] >> j) & 1u) ? p0 : 0.f;
-          p1 = ((keep[ch] >> (j + 1)) & 1u) ? p1 : 0.f;
+          float p0 = fast_exp2(fmaf(__uint_as_float(v[j]), c, neg_m));
+          float p1 = fast_exp2(fmaf(__uint_as_float(v[j + 1]), c, neg_m));
+          if (partial) {
+            p0 = ((keep[ch] >> j) & 1u) ? p0 : 0.f;
+            p1 = ((keep[ch] >> (j + 1)) & 1u) ? p1 : 0.f;
+          }
           rowsum += p0 + p1;
           pk[j >> 1] = pack_bf16(p0, p1);
         }
         tmem_st16(tS + lane_base + ch * 16, pk);
       }
       l = l * alpha + rowsum;
-      m = m_new;
 
-      // rescale the accumulator when some row of this warp moved its maximum
+      // rescale the accumulator when some row of this warp moved its reference maximum
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
@@ -289,7 +308,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
 int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream) {
   const FwdArgs& a = L.args;
-  dim3 grid(a.q_heads, a.list.n_outer_tiles, L.batch);
+  dim3 grid(a.list.n_outer_tiles * L.batch * a.q_heads, 1, 1);
   cudaError_t err;
   if (L.head_dim == 128) {
     constexpr int smem = FwdSmem<128>::kTotal;

@@ -14,9 +14,12 @@ struct ScheduleArgs {
   TokenInfo tok;
   uint32_t* tiles;     // (B, n_outer_tiles, n_inner_tiles)
   int32_t* counts;     // (B, n_outer_tiles)
+  int32_t* order;      // (B * n_outer_tiles) rows sorted by list length, longest first
+  const int4* inner_summary;  // (B, n_inner_tiles) {seg_min, seg_max, pos_min, pos_max}
   int32_t n_outer_tiles, n_inner_tiles;
   int32_t outer_len, inner_len;
 };
+void launch_tile_summaries(const TokenInfo& tok, int batch, int4* q_sum, int4* kv_sum, cudaStream_t s);
 void launch_schedule(bool kv_outer, const ScheduleArgs& a, int batch, cudaStream_t s);
 
 struct FwdArgs {
@@ -29,6 +32,7 @@ struct FwdArgs {
   long long o_strides[3];   // batch, seq, head (elements)
   float scale_log2e;
   int32_t q_heads, group;   // group = Hq / Hkv
+  int32_t batch;
 };
 
 struct FwdLaunch {
@@ -51,6 +55,8 @@ struct BwdArgs {
   long long q_strides[3];
   float scale_log2e, scale;
   int32_t q_heads, kv_heads, group;
+  int32_t debug;            // experiment switches (0 in production)
+  int32_t batch;
 };
 
 struct BwdLaunch {

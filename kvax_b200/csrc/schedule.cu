@@ -1,28 +1,82 @@
 // Tile-list builder: turns a block mask (four bound arrays at the caller's block sizes)
 // into, for every 128-row outer tile, the ascending list of 128-column inner tiles the
-// attention kernels must visit.  A tile whose every element lies in the "full" range of
-// every row is emitted as unmasked; a tile in which no element survives the reference's
-// element-level rule is dropped (it contributes nothing to any row); the rest are
-// emitted as partial and masked per element by the consumer.
+// attention kernels must visit, plus a longest-first launch order of the outer tiles.
 //
-// One CTA of 128 threads per (outer tile, batch); thread t owns outer row t.
+//   * A tile whose every element lies in the "full" range of every row is emitted as
+//     unmasked.
+//   * A tile in which no element survives the reference's element-level rule is dropped
+//     (it contributes nothing to any row).  Most such tiles are rejected by an interval
+//     test on per-tile (segment min/max, position min/max) summaries; the rest by an exact
+//     128 x 128 test.
+//   * Everything else is emitted as partial and masked per element by the consumer.
+//
+// Launches: tile_summary_kernel (one warp per 128-token tile of either side),
+// schedule_kernel (one CTA of 128 threads per (outer tile, batch); thread t owns outer
+// row t), order_kernel (one CTA: counting sort of the outer tiles by list length).
 #include "attn_common.cuh"
 #include "internal.h"
 
 namespace kvx {
 
+namespace {
+
+constexpr int kChunk = 1024;   // inner tiles classified per pass
+
+// ---- per-tile summaries ---------------------------------------------------------------
+// int4 {seg_min, seg_max, pos_min, pos_max} over the valid tokens of a tile; raw segment
+// ids (PAD participates: PAD matches PAD in the element rule).
+__global__ void __launch_bounds__(256) tile_summary_kernel(const TokenInfo tok, int4* q_sum, int4* kv_sum,
+                                                          int n_q_tiles, int n_kv_tiles, int batch) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_q = (long long)batch * n_q_tiles, n_all = n_q + (long long)batch * n_kv_tiles;
+  if (warp >= n_all) return;
+  const bool is_q = warp < n_q;
+  const long long local = is_q ? warp : warp - n_q;
+  const int n_tiles = is_q ? n_q_tiles : n_kv_tiles;
+  const int b = int(local / n_tiles), t = int(local % n_tiles);
+  const int len = is_q ? tok.q_len : tok.kv_len;
+  int smin = INT32_MAX, smax = INT32_MIN, pmin = INT32_MAX, pmax = INT32_MIN;
+  for (int i = t * kTile + lane; i < min((t + 1) * kTile, len); i += 32) {
+    int seg, pos;
+    if (is_q) { seg = __ldg(tok.q_seg + (long long)b * len + i); pos = query_position(tok, b, i); }
+    else { seg = __ldg(tok.kv_seg + (long long)b * len + i); pos = tok.sequential ? i : __ldg(tok.kv_pos + (long long)b * len + i); }
+    smin = min(smin, seg); smax = max(smax, seg); pmin = min(pmin, pos); pmax = max(pmax, pos);
+  }
+  smin = __reduce_min_sync(0xffffffffu, smin); smax = __reduce_max_sync(0xffffffffu, smax);
+  pmin = __reduce_min_sync(0xffffffffu, pmin); pmax = __reduce_max_sync(0xffffffffu, pmax);
+  if (lane == 0) (is_q ? q_sum : kv_sum)[local] = make_int4(smin, smax, pmin, pmax);
+}
+
+__device__ __forceinline__ int block_min(int v, int* s) {
+  v = __reduce_min_sync(0xffffffffu, v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return min(min(s[0], s[1]), min(s[2], s[3]));
+}
+__device__ __forceinline__ int block_max(int v, int* s) {
+  v = __reduce_max_sync(0xffffffffu, v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return max(max(s[0], s[1]), max(s[2], s[3]));
+}
 
 template <bool kKvOuter>
 __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
   __shared__ int s_seg[kTile];
   __shared__ int s_pos[kTile];
-  __shared__ int s_red[4][4];
+  __shared__ int s_red[4];
+  __shared__ int s_red2[4];
+  __shared__ unsigned char s_code[kChunk];    // 0 drop, 1 unmasked, 2 needs the exact test, 3 partial
+  __shared__ int s_count;
   const int t = threadIdx.x;
   const int ot = blockIdx.x, b = blockIdx.y;
   const int o = ot * kTile + t;                       // outer token of this thread
   const bool row_valid = o < a.outer_len;
 
-  RowBounds rb = load_bounds(a.mask, b, min(o, a.outer_len - 1));
+  const RowBounds rb = load_bounds(a.mask, b, min(o, a.outer_len - 1));
   int o_seg = KVAX_B200_PADDING_SEGMENT_ID, o_pos = 0;
   if (row_valid) {
     if (kKvOuter) {
@@ -34,74 +88,150 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
     }
   }
 
-  // CTA-wide: visited range [vis_lo, vis_hi) and the range that is "full" for all rows
+  // CTA-wide ranges on the inner axis (tokens)
   const bool visits = row_valid && rb.up > rb.lo;
-  int vis_lo = visits ? rb.lo : INT32_MAX, vis_hi = visits ? rb.up : 0;
-  int full_lo = row_valid ? rb.lof : 0, full_hi = row_valid ? rb.uf : INT32_MAX;
-  vis_lo = __reduce_min_sync(0xffffffffu, vis_lo);
-  vis_hi = __reduce_max_sync(0xffffffffu, vis_hi);
-  full_lo = __reduce_max_sync(0xffffffffu, full_lo);
-  full_hi = __reduce_min_sync(0xffffffffu, full_hi);
-  if ((t & 31) == 0) {
-    s_red[t >> 5][0] = vis_lo; s_red[t >> 5][1] = vis_hi; s_red[t >> 5][2] = full_lo; s_red[t >> 5][3] = full_hi;
-  }
-  __syncthreads();
-  vis_lo = min(min(s_red[0][0], s_red[1][0]), min(s_red[2][0], s_red[3][0]));
-  vis_hi = max(max(s_red[0][1], s_red[1][1]), max(s_red[2][1], s_red[3][1]));
-  full_lo = max(max(s_red[0][2], s_red[1][2]), max(s_red[2][2], s_red[3][2]));
-  full_hi = min(min(s_red[0][3], s_red[1][3]), min(s_red[2][3], s_red[3][3]));
-  full_hi = min(full_hi, a.inner_len);
-  vis_hi = min(vis_hi, ((a.inner_len + kTile - 1) / kTile) * kTile);
+  const bool has_full = row_valid && rb.uf > rb.lof;
+  const int vis_lo = block_min(visits ? rb.lo : INT32_MAX, s_red);
+  int vis_hi = block_max(visits ? rb.up : 0, s_red);
+  const int all_full_lo = block_max(row_valid ? rb.lof : 0, s_red);         // full for every row
+  const int all_full_hi = min(block_min(row_valid ? rb.uf : INT32_MAX, s_red), a.inner_len);
+  vis_hi = min(vis_hi, a.n_inner_tiles * kTile);
 
   uint32_t* out = a.tiles + ((long long)b * a.n_outer_tiles + ot) * a.n_inner_tiles;
-  int count = 0;
+  if (t == 0) s_count = 0;
+  __syncthreads();
   if (vis_hi > vis_lo) {
     const int it0 = max(vis_lo, 0) / kTile;
     const int it1 = min((vis_hi + kTile - 1) / kTile, a.n_inner_tiles);
-    for (int it = it0; it < it1; ++it) {
-      const int c0 = it * kTile;
-      if (full_lo <= c0 && c0 + kTile <= full_hi) {     // unmasked for every row
-        if (t == 0) out[count] = uint32_t(it);
-        ++count;
-        continue;
-      }
-      // stage the inner tile's segment ids and positions
-      const int i = c0 + t;
-      int seg = KVAX_B200_PADDING_SEGMENT_ID, pos = 0;
-      if (i < a.inner_len) {
-        if (kKvOuter) {
-          seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + i);
-          pos = query_position(a.tok, b, i);
-        } else {
-          seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + i);
-          pos = a.tok.sequential ? i : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + i);
+    const int4* inner_sum = a.inner_summary + (long long)b * a.n_inner_tiles;
+    for (int base = it0; base < it1; base += kChunk) {
+      const int n = min(kChunk, it1 - base);
+      // A: interval classification.  Every thread tests its own row against the summary
+      // of 32 inner tiles at a time; a tile stays a candidate when any row may hold an
+      // allowed element in it.
+      for (int k0 = 0; k0 < n; k0 += 32) {
+        uint32_t pass = 0, sure = 0;
+        if (row_valid) {
+          const int kn = min(32, n - k0);
+          for (int k = 0; k < kn; ++k) {
+            const int c0 = (base + k0 + k) * kTile, c1 = c0 + kTile;
+            const int4 s = __ldg(inner_sum + base + k0 + k);      // {smin, smax, pmin, pmax}
+            const bool in_full = (c0 < rb.uf) && (c1 > rb.lof);
+            const bool seg_in = (s.x <= o_seg) && (o_seg <= s.y);
+            const bool left_ov = (c0 < rb.lof) && (c1 > rb.lo);
+            const bool right_ov = (c0 < rb.up) && (c1 > rb.uf);
+            const bool causal_ok = kKvOuter ? (s.w >= o_pos) : (o_pos >= s.z);
+            const bool cls = kKvOuter ? (right_ov || (left_ov && causal_ok)) : (left_ov || (right_ov && causal_ok));
+            pass |= ((in_full || (seg_in && cls)) ? 1u : 0u) << k;
+            // sufficient condition for "this row has an allowed element in the tile": part of
+            // the tile lies in the row's full range, or the tile is one segment equal to the
+            // row's, lies inside one class of the row and (where that class is causal) every
+            // position in it passes the causal test
+            const bool full_hit = in_full && (max(c0, rb.lof) < a.inner_len);
+            const bool single = (s.x == s.y) && (s.x == o_seg);
+            const bool left_all = (c0 >= rb.lo) && (c1 <= rb.lof);
+            const bool right_all = (c0 >= rb.uf) && (c1 <= rb.up);
+            const bool causal_all = kKvOuter ? (s.z >= o_pos) : (o_pos >= s.w);
+            const bool cls_all = kKvOuter ? (right_all || (left_all && causal_all)) : (left_all || (right_all && causal_all));
+            sure |= ((full_hit || (single && cls_all)) ? 1u : 0u) << k;
+          }
+        }
+        pass = __reduce_or_sync(0xffffffffu, pass);
+        sure = __reduce_or_sync(0xffffffffu, sure);
+        __syncthreads();
+        if ((t & 31) == 0) { s_red[t >> 5] = int(pass); s_red2[t >> 5] = int(sure); }
+        __syncthreads();
+        if (t < 32 && k0 + t < n) {
+          const uint32_t any = uint32_t(s_red[0] | s_red[1] | s_red[2] | s_red[3]);
+          const uint32_t any_sure = uint32_t(s_red2[0] | s_red2[1] | s_red2[2] | s_red2[3]);
+          const int c0 = (base + k0 + t) * kTile;
+          s_code[k0 + t] = (all_full_lo <= c0 && c0 + kTile <= all_full_hi) ? 1
+                           : (((any_sure >> t) & 1u) ? 3 : (((any >> t) & 1u) ? 2 : 0));
         }
       }
-      __syncthreads();                                   // previous iteration's readers are done
-      s_seg[t] = seg; s_pos[t] = pos;
       __syncthreads();
-      int found = 0;
-      if (row_valid) {
-        const int lim = min(kTile, a.inner_len - c0);
-        for (int j = 0; j < lim; ++j) {
-          const bool seg_eq = (s_seg[j] == o_seg);
-          const bool causal = kKvOuter ? (s_pos[j] >= o_pos) : (o_pos >= s_pos[j]);
-          if (element_allowed<kKvOuter>(rb, c0 + j, seg_eq, causal)) { found = 1; break; }
+      // B: exact test of the undecided tiles (CTA-wide, thread t scans the columns for row t)
+      for (int k = 0; k < n; ++k) {
+        if (s_code[k] != 2) continue;                       // uniform: shared memory value
+        const int c0 = (base + k) * kTile;
+        const int i = c0 + t;
+        int seg = KVAX_B200_PADDING_SEGMENT_ID, pos = 0;
+        if (i < a.inner_len) {
+          if (kKvOuter) {
+            seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + i);
+            pos = query_position(a.tok, b, i);
+          } else {
+            seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + i);
+            pos = a.tok.sequential ? i : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + i);
+          }
         }
+        s_seg[t] = seg; s_pos[t] = pos;
+        __syncthreads();
+        int found = 0;
+        if (row_valid) {
+          const int lim = min(kTile, a.inner_len - c0);
+          for (int j = 0; j < lim; ++j) {
+            const bool seg_eq = (s_seg[j] == o_seg);
+            const bool causal = kKvOuter ? (s_pos[j] >= o_pos) : (o_pos >= s_pos[j]);
+            if (element_allowed<kKvOuter>(rb, c0 + j, seg_eq, causal)) { found = 1; break; }
+          }
+        }
+        const int any = __syncthreads_or(found);
+        if (t == 0) s_code[k] = any ? 3 : 0;
       }
-      if (__syncthreads_or(found)) {
-        if (t == 0) out[count] = uint32_t(it) | kPartialBit;
-        ++count;
+      __syncthreads();
+      // C: ordered compaction by warp 0
+      if (t < 32) {
+        int cnt = s_count;
+        for (int k0 = 0; k0 < n; k0 += 32) {
+          const int k = k0 + t;
+          const unsigned char code = (k < n) ? s_code[k] : 0;
+          const unsigned m = __ballot_sync(0xffffffffu, code != 0);
+          if (code != 0) out[cnt + __popc(m & ((1u << t) - 1))] = uint32_t(base + k) | (code == 3 ? kPartialBit : 0u);
+          cnt += __popc(m);
+        }
+        if (t == 0) s_count = cnt;
       }
+      __syncthreads();
     }
   }
-  if (t == 0) a.counts[(long long)b * a.n_outer_tiles + ot] = count;
+  if (t == 0) a.counts[(long long)b * a.n_outer_tiles + ot] = s_count;
+}
+
+// Launch order: outer tiles (all batches) sorted by list length, longest first, so that
+// the tail of a launch is made of short work items.  Counting sort in one CTA.
+constexpr int kBins = 2048;
+__global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int32_t* order, int n_rows) {
+  __shared__ int hist[kBins];
+  for (int i = threadIdx.x; i < kBins; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_rows; i += blockDim.x) atomicAdd(&hist[min(counts[i], kBins - 1)], 1);
+  __syncthreads();
+  // exclusive prefix over descending bins: start[bin] = number of rows with a larger key
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int bin = kBins - 1; bin >= 0; --bin) { const int c = hist[bin]; hist[bin] = run; run += c; }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_rows; i += blockDim.x) {
+    const int pos = atomicAdd(&hist[min(counts[i], kBins - 1)], 1);
+    order[pos] = i;
+  }
+}
+
+}  // namespace
+
+void launch_tile_summaries(const TokenInfo& tok, int batch, int4* q_sum, int4* kv_sum, cudaStream_t s) {
+  const int nq = (tok.q_len + kTile - 1) / kTile, nk = (tok.kv_len + kTile - 1) / kTile;
+  const long long warps = (long long)batch * (nq + nk);
+  tile_summary_kernel<<<int((warps + 7) / 8), 256, 0, s>>>(tok, q_sum, kv_sum, nq, nk, batch);
 }
 
 void launch_schedule(bool kv_outer, const ScheduleArgs& a, int batch, cudaStream_t s) {
   dim3 grid(a.n_outer_tiles, batch);
   if (kv_outer) schedule_kernel<true><<<grid, kTile, 0, s>>>(a);
   else schedule_kernel<false><<<grid, kTile, 0, s>>>(a);
+  order_kernel<<<1, 1024, 0, s>>>(a.counts, a.order, a.n_outer_tiles * batch);
 }
 
 }  // namespace kvx
