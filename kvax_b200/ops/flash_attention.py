@@ -141,15 +141,18 @@ def context_offsets(rank: int, cp: int, local_q_len: int, permuted: bool) -> tup
     return (rank * half, (2 * cp - rank - 1) * half - half)
 
 
-def _gather_kv(x: torch.Tensor, cp: int, group, permuted: bool) -> torch.Tensor:
-    """All-gather of the local (B, S_loc, H, D) slices into (B, S, H, D) in natural order."""
+def _gather_kv(x: torch.Tensor, cp: int, group, permuted: bool, permute_fn=None) -> torch.Tensor:
+    """All-gather of the local (B, S_loc, H, D) slices into (B, S, H, D) in natural order.
+    `permute_fn(tensor, cp, reverse)` defaults to the CUDA chunk-permutation kernel."""
     import torch.distributed as dist
     from kvax_b200.utils.permutation import _permute_one
+    _permute_one = permute_fn or _permute_one
 
     x = x.contiguous()
     B = x.shape[0]
-    gathered = torch.empty((cp,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(gathered, x, group=group)
+    gathered = torch.empty((cp * B,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(gathered, x, group=group)      # rank-major concatenation
+    gathered = gathered.view((cp,) + tuple(x.shape))
     if B == 1:
         full = gathered.view(1, cp * x.shape[1], *x.shape[2:])
     else:
@@ -157,11 +160,12 @@ def _gather_kv(x: torch.Tensor, cp: int, group, permuted: bool) -> torch.Tensor:
     return _permute_one(full, cp, reverse=True) if permuted else full
 
 
-def _scatter_dkv(g: torch.Tensor, cp: int, group, permuted: bool, out_dtype) -> torch.Tensor:
+def _scatter_dkv(g: torch.Tensor, cp: int, group, permuted: bool, out_dtype, permute_fn=None) -> torch.Tensor:
     """Reduce-scatter (fp32 sum) of a natural-order (B, S, H, D) gradient to the slice each
     rank owns, then the cast to the input dtype."""
     import torch.distributed as dist
     from kvax_b200.utils.permutation import _permute_one
+    _permute_one = permute_fn or _permute_one
 
     B, S = g.shape[:2]
     if permuted:
@@ -169,8 +173,8 @@ def _scatter_dkv(g: torch.Tensor, cp: int, group, permuted: bool, out_dtype) -> 
     g = g.view(B, cp, S // cp, *g.shape[2:])
     if B != 1:
         g = g.transpose(0, 1).contiguous()
-    g = g.reshape(cp, B, S // cp, *g.shape[3:])
-    local = torch.empty(g.shape[1:], dtype=g.dtype, device=g.device)
+    g = g.reshape(cp * B, S // cp, *g.shape[3:])
+    local = torch.empty((B,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
     dist.reduce_scatter_tensor(local, g, op=dist.ReduceOp.SUM, group=group)
     return local.to(out_dtype)
 

@@ -1,0 +1,58 @@
+"""Worker of tests/test_context_parallel_cpu.py: world_size ranks on CPU with gloo.
+
+Checks the host-side context-parallel plumbing of flash_attention without a GPU: the
+K/V all-gather into natural order and the dK/dV reduce-scatter back to the owners, with
+the chunk permutation done by the NumPy oracle instead of the CUDA kernel."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from kvax_b200.ops.flash_attention import _gather_kv, _scatter_dkv, context_offsets  # noqa: E402
+from kvax_b200.utils.sharding import Mesh  # noqa: E402
+from oracle import permutation_oracle as po  # noqa: E402
+
+
+def oracle_permute(x, cp, reverse):
+    return torch.from_numpy(po.apply_permutation(x.numpy(), cp, reverse).copy())
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mesh = Mesh(("data", "context"), (1, world))
+    assert mesh.coordinate("context") == rank and mesh.group("context") is None
+    for B in (1, 2):
+        S, H, D = 64 * world, 2, 4
+        g = torch.Generator().manual_seed(7)
+        full = torch.randn(B, S, H, D, generator=g)
+        for permuted in (True, False):
+            glob = oracle_permute(full, world, False) if permuted else full     # what the caller shards
+            loc = S // world
+            mine = glob[:, rank * loc:(rank + 1) * loc].contiguous()
+            got = _gather_kv(mine, world, None, permuted, permute_fn=oracle_permute)
+            assert torch.equal(got, full), f"gather mismatch B={B} permuted={permuted}"
+            # every rank contributes (rank+1) * full as its dK; owners get the sum of their slice
+            grad = (rank + 1.0) * full
+            out = _scatter_dkv(grad, world, None, permuted, torch.float32, permute_fn=oracle_permute)
+            expect = sum(r + 1.0 for r in range(world)) * mine
+            assert torch.allclose(out, expect), f"scatter mismatch B={B} permuted={permuted}"
+            first, second = context_offsets(rank, world, loc, permuted)
+            idx = torch.arange(S).view(1, S, 1, 1).float().expand(B, S, 1, 1)
+            gi = (oracle_permute(idx, world, False) if permuted else idx)[0, rank * loc:(rank + 1) * loc, 0, 0]
+            local = torch.arange(loc).float()
+            glob_idx = torch.where(local * 2 >= loc, local + second, local + first)
+            assert torch.equal(glob_idx, gi), "global offsets do not reproduce global token indices"
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("cp cpu worker ok")
+
+
+if __name__ == "__main__":
+    main()
