@@ -33,7 +33,8 @@ enum {
   KVAX_B200_EUNSUPPORTED = -2,/* shape or dtype outside what the kernels cover        */
   KVAX_B200_EWORKSPACE = -3,  /* workspace too small or misaligned                    */
   KVAX_B200_ELAUNCH = -4,     /* the CUDA runtime refused a launch or a tensor map    */
-  KVAX_B200_ENODEVICE = -5    /* no usable sm_100 device / driver entry point missing */
+  KVAX_B200_ENODEVICE = -5,   /* no usable sm_100 device / driver entry point missing */
+  KVAX_B200_ESCRATCH = -6     /* problem needs more than the library's built-in scratch area */
 };
 
 enum { KVAX_B200_BF16 = 0 };
@@ -78,6 +79,31 @@ typedef struct kvax_b200_mask_params {
 size_t kvax_b200_mask_workspace_bytes(const kvax_b200_mask_params* p);
 int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
                          kvax_b200_stream_t stream);
+
+/* Block-mask builder for callers that cannot hand over device memory of their own.
+ * (No counterpart in the reference: its custom calls get every buffer from XLA.)
+ *
+ * Some hosts of this library may only pass the buffers their framework gave them and
+ * have no way to obtain extra device memory at call time: a custom-call handler that
+ * runs while the framework owns the allocator (its arena is fixed once a program is
+ * compiled), code running inside a region where allocation is forbidden, or a binding
+ * that simply did not declare a workspace result.  For them this entry point does what
+ * kvax_b200_mask_build does, with the per-block summaries kept in a fixed 4 MiB area
+ * inside the library's own device image instead of a caller workspace.  It never calls
+ * cudaMalloc / cudaFree or any allocating routine.
+ *
+ * Limit: kvax_b200_mask_workspace_bytes(p) must not exceed 4 MiB (4194304 bytes), i.e.
+ * the masks of one call may cover at most 262144 blocks counted over both sides and all
+ * masks (batch * (ceil(Sq/q_block) + ceil(Skv/kv_block)) summed over the masks, with
+ * 256-byte rounding per array); beyond that the call returns KVAX_B200_ESCRATCH and
+ * launches nothing.  Every GPU that loads the library holds the 4 MiB until exit.
+ *
+ * The first call on each device looks up the device address of the area (with that
+ * device current); make that first call outside any stream capture.  All calls on a
+ * device share the one area and nothing in it has to start at zero (every summary is
+ * rewritten before it is read), but two calls whose kernels overlap on the GPU — different
+ * streams, no ordering between them — race on it: order them.                          */
+int kvax_b200_mask_build_static(const kvax_b200_mask_params* p, kvax_b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Context-parallel token permutation (pure data movement, bit-exact).

@@ -15,6 +15,7 @@ EXPORTS = (
     "kvax_b200_error_string",
     "kvax_b200_mask_workspace_bytes",
     "kvax_b200_mask_build",
+    "kvax_b200_mask_build_static",
     "kvax_b200_permute_tokens",
     "kvax_b200_attn_fwd_workspace_bytes",
     "kvax_b200_attn_fwd",
@@ -85,6 +86,8 @@ def load() -> C.CDLL:
     lib.kvax_b200_mask_workspace_bytes.argtypes = [C.POINTER(MaskParams)]
     lib.kvax_b200_mask_build.restype = C.c_int
     lib.kvax_b200_mask_build.argtypes = [C.POINTER(MaskParams), vp, C.c_size_t, vp]
+    lib.kvax_b200_mask_build_static.restype = C.c_int
+    lib.kvax_b200_mask_build_static.argtypes = [C.POINTER(MaskParams), vp]
     lib.kvax_b200_permute_tokens.restype = C.c_int
     lib.kvax_b200_permute_tokens.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp]
     lib.kvax_b200_attn_fwd_workspace_bytes.restype = C.c_size_t

@@ -128,6 +128,7 @@ extern "C" const char* kvax_b200_error_string(int code) {
     case KVAX_B200_EWORKSPACE: return "workspace too small or misaligned";
     case KVAX_B200_ELAUNCH: return "CUDA launch or tensor-map creation failed";
     case KVAX_B200_ENODEVICE: return "no usable device or driver entry point";
+    case KVAX_B200_ESCRATCH: return "problem exceeds the library's built-in 4 MiB scratch area; use the workspace variant";
     default: return "unknown error";
   }
 }

@@ -223,3 +223,36 @@ extern "C" int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* worksp
   if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
   return KVAX_B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Variant with built-in scratch memory, for callers that cannot provide a workspace.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+constexpr int kMaxDevices = 64;
+
+// Lives in the library's device image: every GPU that loads the library holds it.
+static __device__ __align__(256) unsigned char g_mask_scratch[kStaticScratchBytes];
+
+// Device address of g_mask_scratch per device.  In host code the symbol's name is only a
+// stand-in; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+void* g_scratch_addr[kMaxDevices] = {};
+
+}  // namespace
+
+extern "C" int kvax_b200_mask_build_static(const kvax_b200_mask_params* p, kvax_b200_stream_t stream) {
+  if (!p) return KVAX_B200_EINVAL;
+  const size_t need = kvax_b200_mask_workspace_bytes(p);
+  if (need == 0) return KVAX_B200_EINVAL;
+  if (need > kStaticScratchBytes) return KVAX_B200_ESCRATCH;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return KVAX_B200_ENODEVICE;
+  void* ptr = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {   // first call on this device (two racing first calls obtain the same address)
+    if (cudaGetSymbolAddress(&ptr, g_mask_scratch) != cudaSuccess || !ptr) return KVAX_B200_ENODEVICE;
+    __atomic_store_n(&g_scratch_addr[dev], ptr, __ATOMIC_RELEASE);
+  }
+  return kvax_b200_mask_build(p, ptr, kStaticScratchBytes, stream);
+}
