@@ -3,7 +3,6 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <string.h>
-#include <stdlib.h>
 
 #include "../../include/kvax_b200.h"
 #include "internal.h"
@@ -176,7 +175,8 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   fill_list(&a.list, sa);
   a.mask = mv; a.tok = sa.tok;
   a.out = static_cast<__nv_bfloat16*>(p->out); a.lse = p->lse; a.status = p->status;
-  for (int i = 0; i < 3; ++i) a.o_strides[i] = s.o_strides[i];
+  a.q = static_cast<const __nv_bfloat16*>(p->q);
+  for (int i = 0; i < 3; ++i) { a.o_strides[i] = s.o_strides[i]; a.q_strides[i] = s.q_strides[i]; }
   a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;
@@ -258,7 +258,6 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   for (int i = 0; i < 3; ++i) a.q_strides[i] = s.q_strides[i];
   a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;
-  { const char* e = getenv("KVAX_B200_DEBUG"); a.debug = e ? atoi(e) : 0; }
   a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;
 

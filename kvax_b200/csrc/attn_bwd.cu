@@ -133,11 +133,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
         tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_x2, &bars[B_XFULL], x * 64, xh, ot * kTile, b);
       }
       bool ok = true;
+      uint32_t e_next = __ldg(list);               // list entries are fetched one iteration ahead
       for (int i = 0; i < n_items && ok; ++i) {
         const int st = i & 1;
-        const int j = kKvOuter ? (i % count) : i;
         const int yh = kKvOuter ? (xh * group + i / count) : (xh / group);
-        const int u = int(__ldg(list + j) & ~kPartialBit);
+        const int u = int(e_next & ~kPartialBit);
+        if (i + 1 < n_items) e_next = __ldg(list + (kKvOuter ? ((i + 1) % count) : (i + 1)));
         if (i >= 2) ok = mbar_wait(&bars[B_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, B_YEMPTY0 + st);
         if (!ok) break;
         uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
@@ -231,32 +232,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       }
     }
     bool ok = true;
-    for (int i = 0; i < n_items && ok; ++i) {
-      const int j = kKvOuter ? (i % count) : i;
-      const uint32_t e = __ldg(list + j);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+    // Per-column info of inner tile `i` (one column per thread of the first half): segment id
+    // and position (partial tiles only) and, for the dK/dV kernel, -LSE2 and delta of the query
+    // rows.  Fetched from global memory one iteration ahead so that the L2 latency is hidden.
+    struct ColInfo { int seg, pos; float nlse, dl; };
+    auto load_cols = [&](int i, uint32_t e) {
+      ColInfo ci{KVAX_B200_PADDING_SEGMENT_ID, 0, -INFINITY, 0.f};
       const bool partial = (e & kPartialBit) != 0;
-      // per-column info of this inner tile (one column per thread of the first half):
-      // segment id and position (partial tiles only) and, for the dK/dV kernel, -LSE2 and
-      // delta of the query rows
-      int* cs = s_cols + (i & 1) * 4 * kTile;
       if ((kKvOuter || partial) && half == 0) {
-        const int col = c0 + row;
-        int seg = KVAX_B200_PADDING_SEGMENT_ID, pos = 0;
-        float nlse = -INFINITY, dl = 0.f;
+        const int col = int(e & ~kPartialBit) * kTile + row;
         if (col < inner_len) {
           if (kKvOuter) {
             const int yh = xh * group + i / count;
             const long long o = ((long long)b * a.q_heads + yh) * a.tok.q_len + col;
-            nlse = -__ldg(a.lse + o); dl = __ldg(a.delta + o);
-            if (partial) { seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + col); pos = query_position(a.tok, b, col); }
+            ci.nlse = -__ldg(a.lse + o); ci.dl = __ldg(a.delta + o);
+            if (partial) { ci.seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + col); ci.pos = query_position(a.tok, b, col); }
           } else {
-            seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + col);
-            pos = a.tok.sequential ? col : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + col);
+            ci.seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + col);
+            ci.pos = a.tok.sequential ? col : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + col);
           }
         }
-        cs[row] = seg; cs[kTile + row] = pos;
-        cs[2 * kTile + row] = __float_as_int(nlse); cs[3 * kTile + row] = __float_as_int(dl);
+      }
+      return ci;
+    };
+    uint32_t e_next = __ldg(list);                 // list entries are fetched two iterations ahead
+    ColInfo ci_next = load_cols(0, e_next);
+    uint32_t e_next2 = (n_items > 1) ? __ldg(list + (kKvOuter ? (1 % count) : 1)) : 0u;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const uint32_t e = e_next;
+      const ColInfo ci = ci_next;
+      const int c0 = int(e & ~kPartialBit) * kTile;
+      const bool partial = (e & kPartialBit) != 0;
+      int* cs = s_cols + (i & 1) * 4 * kTile;
+      if ((kKvOuter || partial) && half == 0) {
+        cs[row] = ci.seg; cs[kTile + row] = ci.pos;
+        cs[2 * kTile + row] = __float_as_int(ci.nlse); cs[3 * kTile + row] = __float_as_int(ci.dl);
+      }
+      if (i + 1 < n_items) {                       // request the next item's info now
+        e_next = e_next2;
+        ci_next = load_cols(i + 1, e_next);
+        if (i + 2 < n_items) e_next2 = __ldg(list + (kKvOuter ? ((i + 2) % count) : (i + 2)));
       }
       mbar_arrive(&bars[B_CFULL]);          // a bounded wait instead of bar.sync: no thread can be left behind
       ok = mbar_wait(&bars[B_CFULL], i & 1, abort_flag, a.status, B_CFULL);

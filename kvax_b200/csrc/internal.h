@@ -26,6 +26,8 @@ struct FwdArgs {
   TileList list;            // one row per query tile
   MaskView mask;            // forward mask (query-outer)
   TokenInfo tok;
+  const __nv_bfloat16* q;   // read directly (rows go to TMEM as the A operand of Q K^T)
+  long long q_strides[3];   // batch, seq, head (elements)
   __nv_bfloat16* out;
   float* lse;               // (B, Hq, Sq)
   int32_t* status;
@@ -55,7 +57,6 @@ struct BwdArgs {
   long long q_strides[3];
   float scale_log2e, scale;
   int32_t q_heads, kv_heads, group;
-  int32_t debug;            // experiment switches (0 in production)
   int32_t batch;
 };
 

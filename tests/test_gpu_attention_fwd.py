@@ -40,7 +40,7 @@ def _check(inp, out, lse, q_slice=None, kv_slice=None):
     ref_o, ref_lse = _oracle(inp, q_slice, kv_slice)
     seg = inp["segment_ids"][:, q_slice or slice(None)]
     rows = (seg != -1)
-    compare("out", out, ref_o, rows[:, :, None, None])
+    compare("out", out, ref_o, rows[:, :, None, None], bf16_output=True)
     lse_rows = rows[:, None, :] & np.isfinite(ref_lse)
     compare("lse2", lse, ref_lse, lse_rows, max_abs=2e-2, rel_l2=1e-3)
 
@@ -114,7 +114,7 @@ def test_forward_llama8b_shape_properties():
     for h in heads:
         ref_o, _ = ao.attention_forward(bf16_round(inp["q"][:, :, h:h + 1]), bf16_round(inp["k"][:, :, h // 4:h // 4 + 1]),
                                         bf16_round(inp["v"][:, :, h // 4:h // 4 + 1]), p, s, p, s, inp["scale"], dtype=np.float32)
-        compare(f"out[h={h}]", out[:, :, h:h + 1], ref_o, (s != -1)[:, :, None, None])
+        compare(f"out[h={h}]", out[:, :, h:h + 1], ref_o, (s != -1)[:, :, None, None], bf16_output=True)
     n_pad = int((s[0] == -1).sum())
     full_pad_tiles = n_pad // 128
     if full_pad_tiles:
