@@ -322,12 +322,32 @@ def main():
             ach = dk_flops / (parts["dkdv_kernel_ms"] * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": "attn_bwd_kernel<128,true> (dK/dV)", "achieved": ach,
                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
-                        "peak_source": peaks["source"] + " burst", "traffic": None,
+                        "peak_source": peaks["source"] + " burst",
+                        # dram__bytes_read.sum + dram__bytes_write.sum of one dK/dV launch on this workload, from
+                        # the ncu capture summarised in profiles/ncu_attn_bwd_c4_docmask_32k.txt (null elsewhere)
+                        "traffic": 7.76e9 if name == "c4_docmask_32k" else None, "traffic_unit": "bytes per launch",
                         "fwd_kernel_tflops": flops_fwd / (parts["fwd_kernel_ms"] * 1e-3) / 1e12,
                         "dq_kernel_tflops": 0.5 * flops_fwd / (parts["dq_kernel_ms"] * 1e-3) / 1e12,
                         "step_frac_of_burst": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                         "step_frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
                         "step_frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / 2250.0}
+
+        # ---- mask builder at a size where bandwidth is measurable (the benchmark
+        #      configurations are <= 2 MiB, i.e. launch bound) -----------------------------
+        mask_info = None
+        if cp == 1:
+            from kvax_b200.ops.mask_creator import build_masks
+            spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
+            mask_info = {"at_workload_us": parts.get("mask_build_ms", 0.0) * 1e3}
+            for (mb, ms_) in ((2048, 4096), (64, 131072)):
+                mp = (torch.arange(ms_, device=dev, dtype=torch.int32) % 1000).repeat(mb, 1)
+                msg = (torch.arange(ms_, device=dev, dtype=torch.int32) // 1000).repeat(mb, 1)
+                build_masks(mp, msg, mp, msg, spec3, True)
+                t_ms = cuda_time(lambda: build_masks(mp, msg, mp, msg, spec3, True), 10)
+                alg = 16.0 * mb * ms_ + 48.0 * mb * ms_ / TILE
+                mask_info[f"B{mb}_S{ms_}"] = {"ms": t_ms, "algorithmic_GBps": alg / (t_ms * 1e-3) / 1e9,
+                                              "frac_of_hbm": alg / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+                del mp, msg
 
         # ---- end to end: pinned host buffers in, results back out, every step ----------
         e2e = None
@@ -389,6 +409,8 @@ def main():
     }
     if roofline:
         line["roofline"] = roofline
+    if cp == 1 and mask_info:
+        line["mask_builder"] = mask_info
     if e2e:
         line["e2e"] = e2e
     if cp == 1 and not args.no_cpu_baseline:

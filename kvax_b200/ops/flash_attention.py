@@ -264,10 +264,18 @@ def flash_attention(
         raise ValueError(f"The case with num_mask_tensors={len(mask)} is not supported.")
     if not query.is_cuda:
         raise _lib.KvaxB200Error("flash_attention needs CUDA tensors (there is no CPU fallback)")
-    if query.dtype != torch.bfloat16 or query.shape[-1] not in _KERNEL_HEAD_DIMS or value.shape[-1] != query.shape[-1]:
+    if query.shape[-1] not in _KERNEL_HEAD_DIMS or value.shape[-1] != query.shape[-1]:
         raise _lib.KvaxB200Error(
-            f"the sm_100a kernels cover bf16 with head_dim in {_KERNEL_HEAD_DIMS} and Dqk == Dv; "
-            f"got {query.dtype}, Dqk={query.shape[-1]}, Dv={value.shape[-1]}")
+            f"the sm_100a kernels cover head_dim in {_KERNEL_HEAD_DIMS} with Dqk == Dv; "
+            f"got Dqk={query.shape[-1]}, Dv={value.shape[-1]}")
+    if query.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise _lib.KvaxB200Error(f"unsupported dtype {query.dtype}")
+    in_dtype = query.dtype
+    if in_dtype != torch.bfloat16:
+        # The kernels compute on bf16 operands with fp32 accumulation.  fp32 / fp16 inputs are
+        # rounded to bf16 first (the reference feeds fp32 to tl.dot, i.e. tf32 tensor cores);
+        # output and gradients come back in the input dtype.
+        query, key, value = query.to(torch.bfloat16), key.to(torch.bfloat16), value.to(torch.bfloat16)
     B, Sq, Hq, _ = query.shape
     if key.shape[0] != B or value.shape[:3] != key.shape[:3] or Hq % key.shape[2]:
         raise AssertionError("inconsistent query / key / value shapes")
@@ -291,7 +299,8 @@ def flash_attention(
     if tuple(kv_positions.shape) != (B, kv_len) or tuple(kv_segment_ids.shape) != (B, kv_len):
         raise AssertionError("kv positions / segment ids must have shape (batch, kv_seq)")
 
-    return _FlashAttention.apply(
+    out = _FlashAttention.apply(
         query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
         _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
         bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
+    return out if in_dtype == torch.bfloat16 else out.to(in_dtype)

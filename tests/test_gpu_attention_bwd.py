@@ -120,3 +120,30 @@ def test_autograd_public_api():
     compare("dq", q.grad.float().cpu().numpy(), rq, rows, bf16_output=True)
     compare("dk", k.grad.float().cpu().numpy(), rk, rows, max_abs=2e-2 + np.abs(rk).max() / 128)
     compare("dv", v.grad.float().cpu().numpy(), rv, rows, max_abs=2e-2 + np.abs(rv).max() / 128)
+
+
+def test_fp32_inputs_tiny_config():
+    """The CPU-runnable configuration (fp32 tensors, D=64, block 64): fp32 inputs go through the
+    bf16 kernels and come back as fp32; compared with the fp32 oracle on the unrounded inputs."""
+    import kvax_b200 as kv
+    inp = _zero_pad_dout(gen.make_inputs(gen.CONFIGS["c1_tiny"], seed=0))
+    q, k, v, do = (torch.from_numpy(inp[n]).cuda() for n in ("q", "k", "v", "dout"))
+    for t in (q, k, v):
+        t.requires_grad_(True)
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(64, 64)
+    mesh = kv.Mesh(("data", "context"), (1, 1))
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        (out * do).sum().backward()
+    assert out.dtype == torch.float32 and q.grad.dtype == torch.float32
+    pp, ss = inp["positions"], inp["segment_ids"]
+    ref_o, _ = ao.attention_forward(inp["q"], inp["k"], inp["v"], pp, ss, pp, ss, inp["scale"], dtype=np.float64)
+    rq, rk, rv = ao.attention_backward(inp["q"], inp["k"], inp["v"], pp, ss, pp, ss, inp["scale"], inp["dout"])
+    rows = (ss != -1)[:, :, None, None]
+    # inputs themselves were rounded to bf16 (relative 2^-9): a wider budget than the bf16-vs-bf16 tests
+    compare("out", out.detach().cpu().numpy(), ref_o, rows, max_abs=3e-2, rel_l2=1e-2)
+    compare("dq", q.grad.cpu().numpy(), rq, rows, max_abs=5e-2, rel_l2=1.5e-2)
+    compare("dk", k.grad.cpu().numpy(), rk, rows, max_abs=5e-2, rel_l2=1.5e-2)
+    compare("dv", v.grad.cpu().numpy(), rv, rows, max_abs=5e-2, rel_l2=1.5e-2)
