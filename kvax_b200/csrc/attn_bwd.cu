@@ -284,18 +284,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (partial) {
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t bits = 0;
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            const int ci = cb + ch * 32 + jj, col = c0 + ci;
-            const bool seg_eq = (cs[ci] == o_seg);
-            const bool causal = kKvOuter ? (cs[kTile + ci] >= o_pos) : (o_pos >= cs[kTile + ci]);
-            const bool al = row_valid && (col < inner_len) && element_allowed<kKvOuter>(rb, col, seg_eq, causal);
-            bits |= (al ? 1u : 0u) << jj;
-          }
-          keep[ch] = bits;
-        }
+        for (int ch = 0; ch < 2; ++ch)
+          keep[ch] = keep_bits32<kKvOuter>(rb, c0 + cb + ch * 32, inner_len, row_valid, o_seg, o_pos, cs + cb + ch * 32,
+                                           cs + kTile + cb + ch * 32);
       }
 
       // ---- P = exp2(S * scale*log2e - LSE2): the 64 values of this thread stay in registers

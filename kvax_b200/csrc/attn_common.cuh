@@ -70,6 +70,69 @@ __device__ __forceinline__ bool element_allowed(const RowBounds& rb, int i, bool
   return in_full || (seg_eq && (in_left || (in_right && causal)));
 }
 
+// Mask bits of one outer row for 32 consecutive inner tokens [i0, i0 + 32): bit j set when
+// element (row, i0 + j) is allowed.  `seg` / `pos` point at the 32 inner segment ids /
+// positions (global or shared memory; `pos` may be null when positions are the token
+// indices).  `o_seg` / `o_pos` belong to the outer row.
+// Fast path: when all four bounds of the row are multiples of 32 (mask block sizes of 32,
+// 64, 128, ...) the whole chunk lies in one class, so the class is resolved once and only
+// the segment and causal comparisons remain per element.
+template <bool kKvOuter>
+__device__ __forceinline__ uint32_t keep_bits32(const RowBounds& rb, int i0, int inner_len, bool row_valid,
+                                                int o_seg, int o_pos, const int32_t* __restrict__ seg,
+                                                const int32_t* __restrict__ pos) {
+  if (!row_valid || i0 >= inner_len) return 0u;
+  const bool whole = (i0 + 32 <= inner_len);
+  if (whole && (((rb.lo | rb.lof | rb.uf | rb.up) & 31) == 0)) {
+    if (i0 >= rb.lof && i0 < rb.uf) return 0xffffffffu;
+    const bool in_left = (i0 >= rb.lo) && (i0 < rb.lof);
+    const bool in_right = (i0 >= rb.uf) && (i0 < rb.up);
+    if (!(in_left || in_right)) return 0u;
+    const bool need_causal = kKvOuter ? in_left : in_right;
+    uint32_t bits = 0;
+    const bool vec = ((reinterpret_cast<uintptr_t>(seg) & 15) == 0) && (!pos || (reinterpret_cast<uintptr_t>(pos) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int4 s4 = *reinterpret_cast<const int4*>(seg + 4 * g);
+        int4 p4 = make_int4(i0 + 4 * g, i0 + 4 * g + 1, i0 + 4 * g + 2, i0 + 4 * g + 3);
+        if (need_causal && pos) p4 = *reinterpret_cast<const int4*>(pos + 4 * g);
+        const int sv[4] = {s4.x, s4.y, s4.z, s4.w};
+        const int pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          bool ok = (sv[t] == o_seg);
+          if (need_causal) ok = ok && (kKvOuter ? (pv[t] >= o_pos) : (o_pos >= pv[t]));
+          bits |= (ok ? 1u : 0u) << (4 * g + t);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        bool ok = (seg[j] == o_seg);
+        if (need_causal) {
+          const int p = pos ? pos[j] : (i0 + j);
+          ok = ok && (kKvOuter ? (p >= o_pos) : (o_pos >= p));
+        }
+        bits |= (ok ? 1u : 0u) << j;
+      }
+    }
+    return bits;
+  }
+  // general path: class resolved per element
+  uint32_t bits = 0;
+#pragma unroll 4
+  for (int j = 0; j < 32; ++j) {
+    const int i = i0 + j;
+    if (i < inner_len) {
+      const int p = pos ? pos[j] : i;
+      const bool causal = kKvOuter ? (p >= o_pos) : (o_pos >= p);
+      bits |= (element_allowed<kKvOuter>(rb, i, seg[j] == o_seg, causal) ? 1u : 0u) << j;
+    }
+  }
+  return bits;
+}
+
 // ---------------------------------------------------------------------------
 // Tile lists (built by schedule.cu): for every (batch, outer tile) the inner tiles to
 // visit, ascending; bit 31 marks tiles that need the element-level mask.

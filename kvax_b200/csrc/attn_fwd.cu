@@ -238,21 +238,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
       if (partial) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t bits = 0;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c0 + ch * 32 + j;
-            bool al = false;
-            if (col < a.tok.kv_len) {
-              const int ks = __ldg(kv_seg + col);
-              const int kp = a.tok.sequential ? col : __ldg(kv_pos + col);
-              al = row_valid && element_allowed<false>(rb, col, ks == q_seg, q_pos >= kp);
-            }
-            bits |= (al ? 1u : 0u) << j;
-          }
-          keep[ch] = bits;
-        }
+        for (int ch = 0; ch < 4; ++ch)
+          keep[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + ch * 32,
+                                        a.tok.sequential ? nullptr : kv_pos + c0 + ch * 32);
       }
 
       ok = mbar_wait(&bars[B_SFULL0 + wg], (it >> 1) & 1, abort_flag, a.status, B_SFULL0 + wg);
