@@ -40,7 +40,7 @@ constexpr int kThreads = (kComputeWarps + 2) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kHalf = kTile / 2;                    // columns handled by one compute thread
 
-enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_SFULL, B_DPFULL, B_PFULL, B_DSFULL, B_ACCFULL, B_CFULL, B_COUNT };
+enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_SFULL0, B_SFULL1, B_DPFULL, B_PFULL0, B_PFULL1, B_DSFULL, B_ACCFULL, B_CFULL, B_COUNT };
 
 template <int D>
 struct BwdSmem {
@@ -48,8 +48,8 @@ struct BwdSmem {
   static constexpr int kBoxBytes = kTile * 64 * 2;
   static constexpr int kX1 = 0, kX2 = kTileBytes;
   static constexpr int kY = 2 * kTileBytes;              // stage s: Y1 at kY + s*2*tile, Y2 right after
-  static constexpr int kCols = 6 * kTileBytes;           // per-column info, 2 buffers x 4 arrays x 128 x 4 B
-  static constexpr int kBars = kCols + 2 * 4 * kTile * 4;
+  static constexpr int kCols = 6 * kTileBytes;           // per-column info, 3 buffers x 4 arrays x 128 x 4 B
+  static constexpr int kBars = kCols + 3 * 4 * kTile * 4;
   static constexpr int kTmemSlot = kBars + 8 * B_COUNT;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4 + 1024;
@@ -110,7 +110,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
 
   if (tid == 0) {
     for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(&bars[i], (i == B_PFULL || i == B_DSFULL || i == B_CFULL) ? kComputeThreads : 1);
+      mbar_init(&bars[i], (i == B_PFULL0 || i == B_PFULL1 || i == B_DSFULL || i == B_CFULL) ? kComputeThreads : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -177,44 +177,84 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       if (ok) {
         tc_fence_after();
         issue_t(tT1, x1, ybase);
-        umma_commit(&bars[B_SFULL]);
+        umma_commit(&bars[B_SFULL0]);
         issue_t(tT2, x2, ybase + L::kTileBytes);
         umma_commit(&bars[B_DPFULL]);
       }
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i & 1;
-        const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
-        const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
-        const uint32_t acc_on = (i > 0) ? 1u : 0u;
-        const bool more = (i + 1 < n_items);
-        ok = mbar_wait(&bars[B_PFULL], i & 1, abort_flag, a.status, B_PFULL);     // P(i) written, S(i) consumed
-        if (!ok) break;
-        tc_fence_after();
-        if (kKvOuter) issue_acc(tAcc1, tT1, y2, acc_on);                            // dV += P^T dO
-        if (more) {
-          ok = mbar_wait(&bars[B_YFULL0 + (st ^ 1)], ((i + 1) >> 1) & 1, abort_flag, a.status, B_YFULL0 + (st ^ 1));
+      if (kKvOuter) {
+        // dK/dV kernel (TMEM is full: one score buffer):  ... | dV(i), T1(i+1) | dK(i), T2(i+1) | ...
+        for (int i = 0; i < n_items && ok; ++i) {
+          const int st = i & 1;
+          const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
+          const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
+          const uint32_t acc_on = (i > 0) ? 1u : 0u;
+          const bool more = (i + 1 < n_items);
+          ok = mbar_wait(&bars[B_PFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_PFULL0 + st);   // P(i) written, S(i) consumed
           if (!ok) break;
           tc_fence_after();
-          issue_t(tT1, x1, y1n);                                                    // scores of item i+1
-          umma_commit(&bars[B_SFULL]);
+          issue_acc(tAcc1, tT1, y2, acc_on);                                          // dV += P^T dO
+          if (more) {
+            ok = mbar_wait(&bars[B_YFULL0 + (st ^ 1)], ((i + 1) >> 1) & 1, abort_flag, a.status, B_YFULL0 + (st ^ 1));
+            if (!ok) break;
+            tc_fence_after();
+            issue_t(tT1, x1, y1n);                                                    // scores of item i+1
+            umma_commit(&bars[B_SFULL0 + (st ^ 1)]);
+          }
+          ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc(tAcc2, tT2, y1, acc_on);                                          // dK += dS^T Q
+          umma_commit(&bars[B_YEMPTY0 + st]);
+          if (more) {
+            issue_t(tT2, x2, y2n);                                                    // dP of item i+1
+            umma_commit(&bars[B_DPFULL]);
+          } else {
+            umma_commit(&bars[B_ACCFULL]);
+          }
         }
-        ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
-        if (!ok) break;
-        tc_fence_after();
-        issue_acc(tAcc2, tT2, y1, acc_on);                                          // dQ += dS K  /  dK += dS^T Q
-        umma_commit(&bars[B_YEMPTY0 + st]);
-        if (more) {
-          issue_t(tT2, x2, y2n);                                                    // dP of item i+1
-          umma_commit(&bars[B_DPFULL]);
-        } else {
-          umma_commit(&bars[B_ACCFULL]);
+      } else {
+        // dQ kernel: the columns of ACC1 are free, so the scores are double-buffered and run a whole
+        // item ahead of the register math:  T1(0) T2(0) T1(1) | dQ(0), T2(1), T1(2) | dQ(1), T2(2), T1(3) | ...
+        if (ok && n_items > 1) {
+          ok = mbar_wait(&bars[B_YFULL1], 0, abort_flag, a.status, B_YFULL1);
+          if (ok) {
+            tc_fence_after();
+            issue_t(tAcc1, x1, ybase + 2 * L::kTileBytes);
+            umma_commit(&bars[B_SFULL1]);
+          }
+        }
+        for (int i = 0; i < n_items && ok; ++i) {
+          const int st = i & 1;
+          const uint32_t y1 = ybase + st * 2 * L::kTileBytes;
+          const uint32_t y2n = ybase + (st ^ 1) * 2 * L::kTileBytes + L::kTileBytes;
+          ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
+          if (!ok) break;
+          tc_fence_after();
+          issue_acc(tAcc2, tT2, y1, (i > 0) ? 1u : 0u);                               // dQ += dS K
+          umma_commit(&bars[B_YEMPTY0 + st]);
+          if (i + 1 < n_items) {
+            issue_t(tT2, x2, y2n);                                                    // dP of item i+1 (its tiles were awaited for T1(i+1))
+            umma_commit(&bars[B_DPFULL]);
+          } else {
+            umma_commit(&bars[B_ACCFULL]);
+          }
+          if (i + 2 < n_items) {
+            ok = mbar_wait(&bars[B_PFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_PFULL0 + st);   // S(i) consumed: buffer st is free
+            if (!ok) break;
+            ok = mbar_wait(&bars[B_YFULL0 + st], ((i + 2) >> 1) & 1, abort_flag, a.status, B_YFULL0 + st);
+            if (!ok) break;
+            tc_fence_after();
+            issue_t(st ? tAcc1 : tT1, x1, y1);                                        // scores of item i+2 (stage st now holds its tiles)
+            umma_commit(&bars[B_SFULL0 + st]);
+          }
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ register math
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t my_t1 = tT1 + lane_base + half * kHalf;      // fp32 columns of this thread; P goes to the first 32 of them
+    const uint32_t my_t1_even = tT1 + lane_base + half * kHalf;   // fp32 columns of this thread; P goes to the first 32 of them
+    const uint32_t my_t1_odd = (kKvOuter ? tT1 : tAcc1) + lane_base + half * kHalf;   // dQ kernel: second score buffer
     const uint32_t my_t2 = tT2 + lane_base + half * kHalf;
     const float c = a.scale_log2e;
     const RowBounds rb = load_bounds(a.mask, b, min(r, outer_len - 1));
@@ -255,27 +295,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       }
       return ci;
     };
-    uint32_t e_next = __ldg(list);                 // list entries are fetched two iterations ahead
-    ColInfo ci_next = load_cols(0, e_next);
-    uint32_t e_next2 = (n_items > 1) ? __ldg(list + (kKvOuter ? (1 % count) : 1)) : 0u;
-    for (int i = 0; i < n_items && ok; ++i) {
-      const uint32_t e = e_next;
-      const ColInfo ci = ci_next;
-      const int c0 = int(e & ~kPartialBit) * kTile;
-      const bool partial = (e & kPartialBit) != 0;
-      int* cs = s_cols + (i & 1) * 4 * kTile;
-      if ((kKvOuter || partial) && half == 0) {
+    // Staging protocol: the info of item i+1 is written to buffer (i+1) % 3 at the start of
+    // iteration i and announced on C_FULL right away, so the wait at the start of iteration
+    // i+1 normally finds it complete.  A buffer is rewritten three items later; every thread
+    // has then passed the C_FULL phase that follows its last read of it.
+    auto stage_cols = [&](int i, uint32_t e, const ColInfo& ci) {
+      if ((kKvOuter || (e & kPartialBit)) && half == 0) {
+        int* cs = s_cols + (i % 3) * 4 * kTile;
         cs[row] = ci.seg; cs[kTile + row] = ci.pos;
         cs[2 * kTile + row] = __float_as_int(ci.nlse); cs[3 * kTile + row] = __float_as_int(ci.dl);
       }
-      if (i + 1 < n_items) {                       // request the next item's info now
-        e_next = e_next2;
-        ci_next = load_cols(i + 1, e_next);
-        if (i + 2 < n_items) e_next2 = __ldg(list + (kKvOuter ? ((i + 2) % count) : (i + 2)));
-      }
-      mbar_arrive(&bars[B_CFULL]);          // a bounded wait instead of bar.sync: no thread can be left behind
+      mbar_arrive(&bars[B_CFULL]);
+    };
+    auto list_at = [&](int i) { return __ldg(list + (kKvOuter ? (i % count) : i)); };
+    uint32_t e_cur = list_at(0);
+    stage_cols(0, e_cur, load_cols(0, e_cur));
+    uint32_t e_next = (n_items > 1) ? list_at(1) : 0u;       // entry i+1
+    ColInfo ci_next = (n_items > 1) ? load_cols(1, e_next) : ColInfo{KVAX_B200_PADDING_SEGMENT_ID, 0, -INFINITY, 0.f};
+    uint32_t e_next2 = (n_items > 2) ? list_at(2) : 0u;      // entry i+2
+    for (int i = 0; i < n_items && ok; ++i) {
+      const uint32_t e = e_cur;
+      const int c0 = int(e & ~kPartialBit) * kTile;
+      const bool partial = (e & kPartialBit) != 0;
+      const int sbuf = i & 1;                                 // score buffer / barrier pair of this item
+      int* cs = s_cols + (i % 3) * 4 * kTile;
       ok = mbar_wait(&bars[B_CFULL], i & 1, abort_flag, a.status, B_CFULL);
       if (!ok) break;
+      if (i + 1 < n_items) {
+        stage_cols(i + 1, e_next, ci_next);
+        e_cur = e_next;
+        if (i + 2 < n_items) {                      // request the info of item i+2 now
+          e_next = e_next2;
+          ci_next = load_cols(i + 2, e_next);
+          if (i + 3 < n_items) e_next2 = list_at(i + 3);
+        }
+      }
       const int cb = half * kHalf;            // first column (within the tile) of this thread
       const float4* cs_nlse = reinterpret_cast<const float4*>(cs + 2 * kTile + cb);
       const float4* cs_dl = reinterpret_cast<const float4*>(cs + 3 * kTile + cb);
@@ -290,9 +344,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       }
 
       // ---- P = exp2(S * scale*log2e - LSE2): the 64 values of this thread stay in registers
-      ok = mbar_wait(&bars[B_SFULL], i & 1, abort_flag, a.status, B_SFULL);
+      ok = mbar_wait(&bars[B_SFULL0 + sbuf], (i >> 1) & 1, abort_flag, a.status, B_SFULL0 + sbuf);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t my_t1 = sbuf ? my_t1_odd : my_t1_even;
       uint32_t v[2][32];
       tmem_ld32(my_t1, v[0]);
       tmem_ld32(my_t1 + 32, v[1]);
@@ -320,7 +375,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       }
       if (kKvOuter) tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars[B_PFULL]);
+      mbar_arrive(&bars[B_PFULL0 + sbuf]);
 
       // ---- dS = P * (dP - delta)
       ok = mbar_wait(&bars[B_DPFULL], i & 1, abort_flag, a.status, B_DPFULL);
