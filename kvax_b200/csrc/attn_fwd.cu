@@ -253,7 +253,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t v[4][32];
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) tmem_ld32(tS + ch * 32, v[ch]);
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains: no serial dependency
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         tmem_ld_wait(v[ch]);
@@ -262,8 +262,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int j = 0; j < 32; ++j) v[ch][j] = ((keep[ch] >> j) & 1u) ? v[ch][j] : 0xff800000u;   // -inf
         }
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) mx = fmax3(mx, __uint_as_float(v[ch][j]), __uint_as_float(v[ch][j + 1]));
+        for (int j = 0; j < 32; j += 8) {
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            mx4[t] = fmax3(mx4[t], __uint_as_float(v[ch][j + 2 * t]), __uint_as_float(v[ch][j + 2 * t + 1]));
+        }
       }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= c;                                  // scale > 0
       float alpha = 1.f;
       if (mx - m > kLazy) {                     // also taken when m is still -inf
@@ -271,7 +276,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         m = mx;
       }
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
-      float rowsum = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t pk[16];
@@ -279,11 +284,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int j = 0; j < 32; j += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch][j]), c, neg_m));       // exp2(-inf) = 0 on masked columns
           const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch][j + 1]), c, neg_m));
-          rowsum += p0 + p1;
+          rs4[(j >> 1) & 3] += p0 + p1;
           pk[j >> 1] = pack_bf16(p0, p1);
         }
         tmem_st16(tS + ch * 16, pk);
       }
+      const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l = l * alpha + rowsum;
 
       // rescale this group's accumulator when some row of the warp moved its reference
