@@ -152,103 +152,78 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       }
     }
   } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
-      constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
-      const uint32_t x1 = smem_u32(smem + L::kX1), x2 = smem_u32(smem + L::kX2);
-      const uint32_t ybase = smem_u32(smem + L::kY);
-      auto issue_t = [&](uint32_t t_addr, uint32_t x, uint32_t y) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
+    static_assert(kKvOuter, "the query-outer pass has a kernel of its own");
+    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
+    constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
+    const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
+    const uint32_t ybase = smem_u32(smem + L::kY);
+    const int n = __shfl_sync(0xffffffffu, n_items, 0);
+    bool ok = true;
+    // `tmem_sync`: the barrier orders TMEM loads / stores of other threads before the MMAs that follow; barriers
+    // completed by TMA alone need no tcgen05 fence.
+    auto wait = [&](int bar, uint32_t parity, bool tmem_sync) {
+      ok = mbar_wait(&bars[bar], parity, abort_flag, a.status, bar);
+      ok = __all_sync(0xffffffffu, ok);
+      if (tmem_sync) tc_fence_after();
+    };
+    auto issue_t = [&](uint32_t t_addr, uint32_t x_lo, uint32_t y_lo) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;
-          umma_ss(t_addr, make_sdesc_sw128(x + off, 16, 1024), make_sdesc_sw128(y + off, 16, 1024), idesc_t, kk > 0);
-        }
-      };
-      // A operand (bf16 pairs in TMEM): K-steps 0-3 at column offset 0, K-steps 4-7 at offset 64
-      auto issue_acc = [&](uint32_t acc_addr, uint32_t a_addr, uint32_t y, uint32_t acc_on) {
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;
+        umma_ss_lo(t_addr, x_lo + off, y_lo + off, idesc_t, kk > 0);
+      }
+    };
+    // A operand (bf16 pairs in TMEM): K-steps 0-3 at column offset 0, K-steps 4-7 at offset 64
+    auto issue_acc = [&](uint32_t acc_addr, uint32_t a_addr, uint32_t y_lo, uint32_t acc_on) {
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(acc_addr, a_addr + (kk >> 2) * kHalf + (kk & 3) * 8, make_sdesc_sw128(y + kk * 16 * 128, L::kBoxBytes, 1024),
-                  idesc_acc, acc_on | (kk > 0));
-      };
-      bool ok = mbar_wait(&bars[B_XFULL], 0, abort_flag, a.status, B_XFULL);
-      if (ok) ok = mbar_wait(&bars[B_YFULL0], 0, abort_flag, a.status, B_YFULL0);
-      if (ok) {
-        tc_fence_after();
-        issue_t(tT1, x1, ybase);
+      for (int kk = 0; kk < kTile / 16; ++kk)
+        umma_ts_lo(acc_addr, a_addr + (kk >> 2) * kHalf + (kk & 3) * 8, y_lo + ((kk * 16 * 128) >> 4), idesc_acc, acc_on | (kk > 0));
+    };
+    wait(B_XFULL, 0, false);
+    if (ok) wait(B_YFULL0, 0, false);
+    if (ok) {
+      if (elect_one()) {
+        issue_t(tT1, x1_lo, sdesc_lo_sw128(ybase, 16));
         umma_commit(&bars[B_SFULL0]);
-        issue_t(tT2, x2, ybase + L::kTileBytes);
+        issue_t(tT2, x2_lo, sdesc_lo_sw128(ybase + L::kTileBytes, 16));
         umma_commit(&bars[B_DPFULL]);
       }
-      if (kKvOuter) {
-        // dK/dV kernel (TMEM is full: one score buffer):  ... | dV(i), T1(i+1) | dK(i), T2(i+1) | ...
-        for (int i = 0; i < n_items && ok; ++i) {
-          const int st = i & 1;
-          const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
-          const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
-          const uint32_t acc_on = (i > 0) ? 1u : 0u;
-          const bool more = (i + 1 < n_items);
-          ok = mbar_wait(&bars[B_PFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_PFULL0 + st);   // P(i) written, S(i) consumed
-          if (!ok) break;
-          tc_fence_after();
-          issue_acc(tAcc1, tT1, y2, acc_on);                                          // dV += P^T dO
-          if (more) {
-            ok = mbar_wait(&bars[B_YFULL0 + (st ^ 1)], ((i + 1) >> 1) & 1, abort_flag, a.status, B_YFULL0 + (st ^ 1));
-            if (!ok) break;
-            tc_fence_after();
-            issue_t(tT1, x1, y1n);                                                    // scores of item i+1
-            umma_commit(&bars[B_SFULL0 + (st ^ 1)]);
-          }
-          ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
-          if (!ok) break;
-          tc_fence_after();
-          issue_acc(tAcc2, tT2, y1, acc_on);                                          // dK += dS^T Q
-          umma_commit(&bars[B_YEMPTY0 + st]);
-          if (more) {
-            issue_t(tT2, x2, y2n);                                                    // dP of item i+1
-            umma_commit(&bars[B_DPFULL]);
-          } else {
-            umma_commit(&bars[B_ACCFULL]);
-          }
+      __syncwarp();
+    }
+    // TMEM is full (T1 | T2 | dV | dK), so there is one score buffer:  ... | dV(i), T1(i+1) | dK(i), T2(i+1) | ...
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i & 1;
+      const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
+      const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
+      const uint32_t acc_on = (i > 0) ? 1u : 0u;
+      const bool more = (i + 1 < n);
+      wait(B_PFULL0 + st, (i >> 1) & 1, true);                                      // P(i) written, S(i) consumed
+      if (!ok) break;
+      if (elect_one()) issue_acc(tAcc1, tT1, sdesc_lo_sw128(y2, L::kBoxBytes), acc_on);   // dV += P^T dO
+      __syncwarp();
+      if (more) {
+        wait(B_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
+        if (!ok) break;
+        if (elect_one()) {
+          issue_t(tT1, x1_lo, sdesc_lo_sw128(y1n, 16));                             // scores of item i+1
+          umma_commit(&bars[B_SFULL0 + (st ^ 1)]);
         }
-      } else {
-        // dQ kernel: the columns of ACC1 are free, so the scores are double-buffered and run a whole
-        // item ahead of the register math:  T1(0) T2(0) T1(1) | dQ(0), T2(1), T1(2) | dQ(1), T2(2), T1(3) | ...
-        if (ok && n_items > 1) {
-          ok = mbar_wait(&bars[B_YFULL1], 0, abort_flag, a.status, B_YFULL1);
-          if (ok) {
-            tc_fence_after();
-            issue_t(tAcc1, x1, ybase + 2 * L::kTileBytes);
-            umma_commit(&bars[B_SFULL1]);
-          }
-        }
-        for (int i = 0; i < n_items && ok; ++i) {
-          const int st = i & 1;
-          const uint32_t y1 = ybase + st * 2 * L::kTileBytes;
-          const uint32_t y2n = ybase + (st ^ 1) * 2 * L::kTileBytes + L::kTileBytes;
-          ok = mbar_wait(&bars[B_DSFULL], i & 1, abort_flag, a.status, B_DSFULL);   // dS(i) written
-          if (!ok) break;
-          tc_fence_after();
-          issue_acc(tAcc2, tT2, y1, (i > 0) ? 1u : 0u);                               // dQ += dS K
-          umma_commit(&bars[B_YEMPTY0 + st]);
-          if (i + 1 < n_items) {
-            issue_t(tT2, x2, y2n);                                                    // dP of item i+1 (its tiles were awaited for T1(i+1))
-            umma_commit(&bars[B_DPFULL]);
-          } else {
-            umma_commit(&bars[B_ACCFULL]);
-          }
-          if (i + 2 < n_items) {
-            ok = mbar_wait(&bars[B_PFULL0 + st], (i >> 1) & 1, abort_flag, a.status, B_PFULL0 + st);   // S(i) consumed: buffer st is free
-            if (!ok) break;
-            ok = mbar_wait(&bars[B_YFULL0 + st], ((i + 2) >> 1) & 1, abort_flag, a.status, B_YFULL0 + st);
-            if (!ok) break;
-            tc_fence_after();
-            issue_t(st ? tAcc1 : tT1, x1, y1);                                        // scores of item i+2 (stage st now holds its tiles)
-            umma_commit(&bars[B_SFULL0 + st]);
-          }
+        __syncwarp();
+      }
+      wait(B_DSFULL, i & 1, true);                                                  // dS(i) written
+      if (!ok) break;
+      if (elect_one()) {
+        issue_acc(tAcc2, tT2, sdesc_lo_sw128(y1, L::kBoxBytes), acc_on);            // dK += dS^T Q
+        umma_commit(&bars[B_YEMPTY0 + st]);
+        if (more) {
+          issue_t(tT2, x2_lo, sdesc_lo_sw128(y2n, 16));                             // dP of item i+1
+          umma_commit(&bars[B_DPFULL]);
+        } else {
+          umma_commit(&bars[B_ACCFULL]);
         }
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ register math
@@ -469,6 +444,296 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// dQ kernel (query-outer).  Same building blocks as the template above, with a pipeline of
+// its own that the free TMEM columns make possible:
+//   * K runs through a three-stage ring, V through a two-stage ring (V is only needed for dP);
+//   * the scores are double-buffered (T1a / T1b) and issued two items ahead;
+//   * dS(i) is written over the consumed scores S(i) instead of over dP(i), so dP(i+1) does
+//     not wait for the dQ MMAs of item i:
+//         T1(0) T2(0) T1(1) | T2(1), dQ(0), T1(2) | T2(2), dQ(1), T1(3) | ...
+//   * LSE2 and delta are per-row scalars here, and the segment ids / positions of partial
+//     tiles are read straight from global memory, so there is no per-item staging barrier.
+// TMEM: T1a | T2 | T1b | dQ.  Shared memory: Q, dO 2 x 32 KB + K 3 x 32 KB + V 2 x 32 KB.
+// ---------------------------------------------------------------------------------------
+constexpr int kDqKStages = 3, kDqVStages = 2;
+enum DqBar {
+  Q_XFULL = 0, Q_KFULL0, Q_KFULL1, Q_KFULL2, Q_KEMPTY0, Q_KEMPTY1, Q_KEMPTY2,
+  Q_VFULL0, Q_VFULL1, Q_VEMPTY0, Q_VEMPTY1, Q_SFULL0, Q_SFULL1, Q_DPFULL, Q_DSFULL, Q_ACCFULL, Q_COUNT
+};
+
+template <int D>
+struct DqSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kBoxBytes = kTile * 64 * 2;
+  static constexpr int kX1 = 0, kX2 = kTileBytes;
+  static constexpr int kK = 2 * kTileBytes;
+  static constexpr int kV = kK + kDqKStages * kTileBytes;
+  static constexpr int kBars = kV + kDqVStages * kTileBytes;
+  static constexpr int kTmemSlot = kBars + 8 * Q_COUNT;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kTotal = kAbort + 4 + 1024;
+  static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                   const BwdArgs a) {
+  using L = DqSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbort);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int row_rank, h;
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.q_heads, &row_rank, &h);
+  const long long list_row = __ldg(a.list.order + row_rank);     // longest lists first
+  const int b = int(list_row / a.list.n_outer_tiles), qt = int(list_row % a.list.n_outer_tiles);
+  const int kvh = h / a.group;
+  const int n_items = __ldg(a.list.counts + list_row);
+  const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
+
+  const int row = tid & (kTile - 1);
+  const int half = (tid >> 7) & 1;
+  const int r = qt * kTile + row;
+  const bool is_compute = tid < kComputeThreads;
+  const bool row_valid = is_compute && (r < a.tok.q_len);
+  __nv_bfloat16* dq_row = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)h * a.q_strides[2] + half * (D / 2);
+
+  if (n_items == 0) {
+    if (row_valid) {
+      uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) reinterpret_cast<uint4*>(dq_row)[i] = z;
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int i = 0; i < Q_COUNT; ++i) mbar_init(&bars[i], i == Q_DSFULL ? kComputeThreads : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tT1a = tmem_base, tT2 = tmem_base + kTile, tT1b = tmem_base + 2 * kTile, tAcc = tmem_base + 3 * kTile;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(&bars[Q_XFULL], 2 * L::kTileBytes);
+#pragma unroll
+      for (int x = 0; x < D / 64; ++x) {
+        tma_load_4d(smem + L::kX1 + x * L::kBoxBytes, &tmap_q, &bars[Q_XFULL], x * 64, h, qt * kTile, b);
+        tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_do, &bars[Q_XFULL], x * 64, h, qt * kTile, b);
+      }
+      bool ok = true;
+      uint32_t e_next = __ldg(list);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int u = int(e_next & ~kPartialBit);
+        if (i + 1 < n_items) e_next = __ldg(list + i + 1);
+        const int ks = i % kDqKStages, kuse = i / kDqKStages;
+        if (kuse > 0) ok = mbar_wait(&bars[Q_KEMPTY0 + ks], (kuse - 1) & 1, abort_flag, a.status, Q_KEMPTY0 + ks);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars[Q_KFULL0 + ks], L::kTileBytes);
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x)
+          tma_load_4d(smem + L::kK + ks * L::kTileBytes + x * L::kBoxBytes, &tmap_k, &bars[Q_KFULL0 + ks], x * 64, kvh, u * kTile, b);
+        const int vs = i % kDqVStages, vuse = i / kDqVStages;
+        if (vuse > 0) ok = mbar_wait(&bars[Q_VEMPTY0 + vs], (vuse - 1) & 1, abort_flag, a.status, Q_VEMPTY0 + vs);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&bars[Q_VFULL0 + vs], L::kTileBytes);
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x)
+          tma_load_4d(smem + L::kV + vs * L::kTileBytes + x * L::kBoxBytes, &tmap_v, &bars[Q_VFULL0 + vs], x * 64, kvh, u * kTile, b);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
+    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
+    constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
+    const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
+    const uint32_t kbase = smem_u32(smem + L::kK), vbase = smem_u32(smem + L::kV);
+    const int n = __shfl_sync(0xffffffffu, n_items, 0);
+    bool ok = true;
+    // `tmem_sync`: the barrier orders TMEM loads / stores of other threads before the MMAs that follow; barriers
+    // completed by TMA alone need no tcgen05 fence.
+    auto wait = [&](int bar, uint32_t parity, bool tmem_sync) {
+      ok = mbar_wait(&bars[bar], parity, abort_flag, a.status, bar);
+      ok = __all_sync(0xffffffffu, ok);
+      if (tmem_sync) tc_fence_after();
+    };
+    auto issue_t = [&](uint32_t t_addr, uint32_t x_lo, uint32_t y_lo) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;
+        umma_ss_lo(t_addr, x_lo + off, y_lo + off, idesc_t, kk > 0);
+      }
+    };
+    auto issue_t1 = [&](int i) {               // scores of item i into buffer i & 1
+      const int ks = i % kDqKStages;
+      wait(Q_KFULL0 + ks, (i / kDqKStages) & 1, false);
+      if (!ok) return;
+      const uint32_t k_lo = sdesc_lo_sw128(kbase + ks * L::kTileBytes, 16);
+      if (elect_one()) {
+        issue_t((i & 1) ? tT1b : tT1a, x1_lo, k_lo);
+        umma_commit(&bars[Q_SFULL0 + (i & 1)]);
+      }
+      __syncwarp();
+    };
+    auto issue_t2 = [&](int i) {               // dP of item i
+      const int vs = i % kDqVStages;
+      wait(Q_VFULL0 + vs, (i / kDqVStages) & 1, false);
+      if (!ok) return;
+      const uint32_t v_lo = sdesc_lo_sw128(vbase + vs * L::kTileBytes, 16);
+      if (elect_one()) {
+        issue_t(tT2, x2_lo, v_lo);
+        umma_commit(&bars[Q_DPFULL]);
+        umma_commit(&bars[Q_VEMPTY0 + vs]);
+      }
+      __syncwarp();
+    };
+    wait(Q_XFULL, 0, false);
+    if (ok) issue_t1(0);
+    if (ok) issue_t2(0);
+    if (ok && n > 1) issue_t1(1);
+    for (int i = 0; i < n && ok; ++i) {
+      wait(Q_DSFULL, i & 1, true);                   // dS(i) written; dP(i), S(i) consumed
+      if (!ok) break;
+      if (i + 1 < n) issue_t2(i + 1);
+      if (!ok) break;
+      const int ks = i % kDqKStages;
+      const uint32_t ds_addr = (i & 1) ? tT1b : tT1a;
+      const uint32_t k_lo = sdesc_lo_sw128(kbase + ks * L::kTileBytes, L::kBoxBytes);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)                                      // dQ += dS K
+          umma_ts_lo(tAcc, ds_addr + (kk >> 2) * kHalf + (kk & 3) * 8, k_lo + ((kk * 16 * 128) >> 4), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars[Q_KEMPTY0 + ks]);
+        if (i + 1 >= n) umma_commit(&bars[Q_ACCFULL]);
+      }
+      __syncwarp();
+      if (i + 2 < n) issue_t1(i + 2);          // over dS(i): after the dQ MMAs of item i in issue order
+    }
+  } else {
+    // ------------------------------------------------------------------ register math
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const int cb = half * kHalf;
+    const float c = a.scale_log2e;
+    const RowBounds rb = load_bounds(a.mask, b, min(r, a.tok.q_len - 1));
+    int q_seg = KVAX_B200_PADDING_SEGMENT_ID, q_pos = 0;
+    float neg_lse = 0.f, delta = 0.f;
+    if (row_valid) {
+      q_seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + r);
+      q_pos = query_position(a.tok, b, r);
+      neg_lse = -__ldg(a.lse + ((long long)b * a.q_heads + h) * a.tok.q_len + r);
+      delta = __ldg(a.delta + ((long long)b * a.q_heads + h) * a.tok.q_len + r);
+    }
+    const int32_t* kv_seg = a.tok.kv_seg + (long long)b * a.tok.kv_len;
+    const int32_t* kv_pos = a.tok.kv_pos + (long long)b * a.tok.kv_len;
+    bool ok = true;
+    uint32_t e_next = __ldg(list);
+    for (int i = 0; i < n_items && ok; ++i) {
+      const uint32_t e = e_next;
+      if (i + 1 < n_items) e_next = __ldg(list + i + 1);
+      const int c0 = int(e & ~kPartialBit) * kTile;
+      const bool partial = (e & kPartialBit) != 0;
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
+      if (partial) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+          keep[ch] = keep_bits32<false>(rb, c0 + cb + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + cb + ch * 32,
+                                        a.tok.sequential ? nullptr : kv_pos + c0 + cb + ch * 32);
+      }
+      const int sbuf = i & 1;
+      const uint32_t my_t1 = (sbuf ? tT1b : tT1a) + lane_base + cb;
+      const uint32_t my_t2 = tT2 + lane_base + cb;
+
+      // ---- P = exp2(S * scale*log2e - LSE2)
+      ok = mbar_wait(&bars[Q_SFULL0 + sbuf], (i >> 1) & 1, abort_flag, a.status, Q_SFULL0 + sbuf);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[2][32];
+      tmem_ld32(my_t1, v[0]);
+      tmem_ld32(my_t1 + 32, v[1]);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        tmem_ld_wait(v[ch]);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj]), c, neg_lse));
+          if (partial) pv = ((keep[ch] >> jj) & 1u) ? pv : 0.f;
+          v[ch][jj] = __float_as_uint(pv);
+        }
+      }
+
+      // ---- dS = P * (dP - delta), written over the consumed scores of this item
+      ok = mbar_wait(&bars[Q_DPFULL], i & 1, abort_flag, a.status, Q_DPFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dp[2][32];
+      tmem_ld32(my_t2, dp[0]);
+      tmem_ld32(my_t2 + 32, dp[1]);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        tmem_ld_wait(dp[ch]);
+        uint32_t ds[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const float d0 = __uint_as_float(v[ch][jj]) * (__uint_as_float(dp[ch][jj]) - delta);
+          const float d1 = __uint_as_float(v[ch][jj + 1]) * (__uint_as_float(dp[ch][jj + 1]) - delta);
+          ds[jj >> 1] = pack_bf16(d0, d1);
+        }
+        tmem_st16(my_t1 + ch * 16, ds);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[Q_DSFULL]);
+    }
+
+    if (ok) ok = mbar_wait(&bars[Q_ACCFULL], 0, abort_flag, a.status, Q_ACCFULL);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int ch = 0; ch < D / 64; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tAcc + lane_base + half * (D / 2) + ch * 32, v);
+        tmem_ld_wait(v);
+        if (row_valid) {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(v[jj + 0]) * a.scale, __uint_as_float(v[jj + 1]) * a.scale);
+            w.y = pack_bf16(__uint_as_float(v[jj + 2]) * a.scale, __uint_as_float(v[jj + 3]) * a.scale);
+            w.z = pack_bf16(__uint_as_float(v[jj + 4]) * a.scale, __uint_as_float(v[jj + 5]) * a.scale);
+            w.w = pack_bf16(__uint_as_float(v[jj + 6]) * a.scale, __uint_as_float(v[jj + 7]) * a.scale);
+            reinterpret_cast<uint4*>(dq_row)[(ch * 32 + jj) >> 3] = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) {
+    if (*abort_flag && lane == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // delta[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]   (fp32), HBM-bound.
 // D/8 lanes per row (16-byte loads), 32 / (D/8) rows per warp.
 template <int D>
@@ -515,11 +780,22 @@ int launch_bwd(const BwdLaunch& L, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
 
+
+template <int D>
+int launch_dq(const BwdLaunch& L, cudaStream_t stream) {
+  constexpr int smem = DqSmem<D>::kTotal;
+  auto kern = attn_bwd_dq_kernel<D>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
+  dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.q_heads, 1, 1);
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // Q, dO, K, V
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
 }  // namespace
 
 int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream) {
-  if (L.head_dim == 128) return kv_outer ? launch_bwd<128, true>(L, stream) : launch_bwd<128, false>(L, stream);
-  if (L.head_dim == 64) return kv_outer ? launch_bwd<64, true>(L, stream) : launch_bwd<64, false>(L, stream);
+  if (L.head_dim == 128) return kv_outer ? launch_bwd<128, true>(L, stream) : launch_dq<128>(L, stream);
+  if (L.head_dim == 64) return kv_outer ? launch_bwd<64, true>(L, stream) : launch_dq<64>(L, stream);
   return KVAX_B200_EUNSUPPORTED;
 }
 

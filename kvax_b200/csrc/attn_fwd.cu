@@ -163,47 +163,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
   } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);   // Q (K-major) x K (K-major)
-      constexpr uint32_t idesc_o = make_idesc_bf16(kTile, D, 0, 1);       // P (TMEM)    x V (N-major)
-      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      bool ok = true;
-      auto issue_qk = [&](int it) {            // scores of list entry `it` into buffer it & 1
-        const int st = it % kKStages, use = it / kKStages;
-        ok = mbar_wait(&bars[B_KFULL0 + st], use & 1, abort_flag, a.status, B_KFULL0 + st);
-        if (!ok) return;
-        tc_fence_after();
-        const uint32_t ts = tmem_base + (it & 1) * kTile;
-        const uint32_t kb = k_addr + st * L::kTileBytes;
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
+    constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);   // Q (K-major) x K (K-major)
+    constexpr uint32_t idesc_o = make_idesc_bf16(kTile, D, 0, 1);       // P (TMEM)    x V (N-major)
+    const uint32_t q_lo = sdesc_lo_sw128(smem_u32(sQ), 16);
+    const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+    const int n = __shfl_sync(0xffffffffu, count, 0);
+    bool ok = true;
+    // `tmem_sync`: the barrier orders TMEM loads / stores of other threads before the MMAs that follow; barriers
+    // completed by TMA alone need no tcgen05 fence.
+    auto wait = [&](int bar, uint32_t parity, bool tmem_sync) {
+      ok = mbar_wait(&bars[bar], parity, abort_flag, a.status, bar);
+      ok = __all_sync(0xffffffffu, ok);
+      if (tmem_sync) tc_fence_after();
+    };
+    auto issue_qk = [&](int it) {            // scores of list entry `it` into buffer it & 1
+      const int st = it % kKStages, use = it / kKStages;
+      wait(B_KFULL0 + st, use & 1, false);
+      if (!ok) return;
+      const uint32_t ts = tmem_base + (it & 1) * kTile;
+      const uint32_t k_lo = sdesc_lo_sw128(k_addr + st * L::kTileBytes, 16);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kBoxBytes + (kk & 3) * 32;   // 16 bf16 = 32 B inside a 128 B row
-          umma_ss(ts, make_sdesc_sw128(q_addr + off, 16, 1024), make_sdesc_sw128(kb + off, 16, 1024), idesc_s, kk > 0);
+          const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;   // 16 bf16 = 32 B inside a 128 B row
+          umma_ss_lo(ts, q_lo + off, k_lo + off, idesc_s, kk > 0);
         }
         umma_commit(&bars[B_SFULL0 + (it & 1)]);      // also tells the K producer that stage `st` is free
-      };
-      ok = mbar_wait(&bars[B_QFULL], 0, abort_flag, a.status, B_QFULL);
-      if (ok) issue_qk(0);
-      if (ok && count > 1) issue_qk(1);
-      for (int it = 0; it < count && ok; ++it) {
-        const int g = it & 1, vs = it % kVStages, vuse = it / kVStages;
-        ok = mbar_wait(&bars[B_PFULL0 + g], (it >> 1) & 1, abort_flag, a.status, B_PFULL0 + g);
-        if (!ok) break;
-        ok = mbar_wait(&bars[B_VFULL0 + vs], vuse & 1, abort_flag, a.status, B_VFULL0 + vs);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t tp = tmem_base + g * kTile;
-        const uint32_t vb = v_addr + vs * L::kTileBytes;
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          // 16 kv rows per step: rows are 128 B apart, d columns 0-63 / 64-127 in separate boxes
-          const uint64_t vdesc = make_sdesc_sw128(vb + kk * 16 * 128, L::kBoxBytes, 1024);
-          umma_ts(tO + g * kTile, tp + kk * 8, vdesc, idesc_o, (it > 1 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&bars[B_VEMPTY0 + vs]);           // V stage free; P V(it) done (rescale, epilogue)
-        if (it + 2 < count) issue_qk(it + 2);   // reuses buffer g: issued after PV(it), which read P(it)
       }
+      __syncwarp();
+    };
+    wait(B_QFULL, 0, false);
+    if (ok) issue_qk(0);
+    if (ok && n > 1) issue_qk(1);
+    for (int it = 0; it < n && ok; ++it) {
+      const int g = it & 1, vs = it % kVStages, vuse = it / kVStages;
+      wait(B_VFULL0 + vs, vuse & 1, false);
+      if (!ok) break;
+      wait(B_PFULL0 + g, (it >> 1) & 1, true);
+      if (!ok) break;
+      const uint32_t tp = tmem_base + g * kTile;
+      // 16 kv rows per step: rows are 128 B apart, d columns 0-63 / 64-127 in separate boxes
+      const uint32_t v_lo = sdesc_lo_sw128(v_addr + vs * L::kTileBytes, L::kBoxBytes);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts_lo(tO + g * kTile, tp + kk * 8, v_lo + ((kk * 16 * 128) >> 4), idesc_o, (it > 1 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars[B_VEMPTY0 + vs]);           // V stage free; P V(it) done (rescale, epilogue)
+      }
+      __syncwarp();
+      if (it + 2 < n) issue_qk(it + 2);   // reuses buffer g: issued after PV(it), which read P(it)
     }
   } else {
     // ------------------------------------------------------------------ softmax groups + epilogue

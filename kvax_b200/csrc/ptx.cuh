@@ -145,6 +145,16 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One lane of a converged warp.  The MMA-issuing warp runs its loop with all 32 lanes (waits,
+// address arithmetic) and only the tcgen05.mma / tcgen05.commit instructions sit under this
+// predicate: a loop that lives inside an `if (lane == 0)` branch issues several times slower as
+// soon as other warps share its scheduler, because every descriptor then takes a chain of
+// per-thread instructions instead of warp-uniform ones.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 // Arrive on `bar` once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
@@ -167,6 +177,36 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
                                                      uint32_t sbo_bytes) {
   return uint64_t((smem_addr & 0x3ffff) >> 4) | (uint64_t((lbo_bytes >> 4) & 0x3fff) << 16) |
          (uint64_t((sbo_bytes >> 4) & 0x3fff) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// The same descriptor split into its two words, so that an issue loop adds a K-step offset to
+// the low word with one integer add and the high word stays a constant (SBO = 1024 bytes):
+// the single issuing thread otherwise spends more cycles building descriptors than the tensor
+// pipe needs to run the MMA.
+__device__ __forceinline__ uint32_t sdesc_lo_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+constexpr uint32_t kSdescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %4};\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kSdescHiSw128), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(kSdescHiSw128), "r"(accumulate)
+      : "memory");
 }
 
 // ---------------------------------------------------------------------------
