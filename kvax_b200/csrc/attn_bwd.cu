@@ -1,27 +1,24 @@
 // Flash-attention backward for sm_100a (B200): delta preprocess, dQ kernel, dK/dV kernel.
 //
-// The two main kernels are instances of one template.  An "outer" 128-row tile stays
-// resident in shared memory (dQ kernel: the Q and dO tiles of one query tile and head;
-// dK/dV kernel: the K and V tiles of one kv tile and kv head) while "inner" tiles stream
-// through a two-stage TMA pipeline (dQ kernel: K and V tiles of the list of kv tiles;
-// dK/dV kernel: Q and dO tiles of every query head of the group times the list of query
-// tiles).  Per inner tile:
+// Both main kernels keep an "outer" 128-row tile resident in shared memory (dQ kernel: the
+// Q and dO tiles of one query tile and head; dK/dV kernel: the K and V tiles of one kv tile
+// and kv head) while "inner" tiles stream through TMA rings (dQ kernel: K and V tiles of the
+// list of kv tiles; dK/dV kernel: Q and dO tiles of every query head of the group times the
+// list of query tiles).  Per inner tile:
 //     T1 = X1 * Y1^T   (scores:  Q K^T   or  K Q^T)        tcgen05, both operands smem
 //     T2 = X2 * Y2^T   (dP:      dO V^T  or  V dO^T)       tcgen05, both operands smem
 //     P  = exp2(T1 * scale*log2e - LSE2), masked;  dS = P * (T2 - delta)   (registers)
-//     P, dS -> bf16 -> TMEM over T1, T2
-//     ACC1 += P  * Y2   (dV += P^T dO;  dK/dV kernel only)  tcgen05, A from TMEM
-//     ACC2 += dS * Y1   (dQ += dS K  or  dK += dS^T Q)      tcgen05, A from TMEM
-// Warps 0-3 do the register math (thread t = outer row t = TMEM lane t), warp 4 is the
-// TMA producer, warp 5 issues the MMAs.  The MMA order is software-pipelined so that the
-// tensor pipe always has work while the register math of the neighbouring step runs:
-//     ... | ACC1(i), T1(i+1) | ACC2(i), T2(i+1) | ACC1(i+1), T1(i+2) | ...
-// T1(i+1) may overwrite the P(i) columns because tcgen05.mma instructions of one thread
-// execute in issue order and ACC1(i) (the reader of P(i)) is issued first; likewise
-// T2(i+1) after ACC2(i).  The query heads of a GQA group are accumulated
-// on chip by the dK/dV kernel, so dK/dV leave the kernel already summed over the group
-// (the reference sums a (B, Hq, Skv, D) fp32 temporary afterwards,
-// kvax/ops/flash_attention_triton.py:1855-1868).
+//     P, dS -> bf16 -> TMEM
+//     dV += P^T dO (dK/dV kernel);  dQ += dS K  or  dK += dS^T Q   tcgen05, A from TMEM
+// Warps 0-7 do the register math (thread t: outer row t % 128 = TMEM lane, column half
+// t / 128 of every tile), warp 8 is the TMA producer, warp 9 issues the MMAs: the whole warp
+// runs the issue loop and one elected lane executes the tcgen05 instructions.  The MMA
+// order is software-pipelined so that the tensor pipe has work while the register math of
+// the neighbouring step runs; tcgen05.mma instructions of one thread execute in issue
+// order, which is what lets a later MMA overwrite TMEM columns an earlier one reads.
+// The query heads of a GQA group are accumulated on chip by the dK/dV kernel, so dK/dV
+// leave the kernel already summed over the group (the reference sums a (B, Hq, Skv, D) fp32
+// temporary afterwards, kvax/ops/flash_attention_triton.py:1855-1868).
 //
 // Semantics follow flash_attention_backward_kernel_dquery (:620-871),
 // flash_attention_backward_kernel_dkdv (:874-1191) and attn_bwd_preprocess (:373-410).
@@ -40,31 +37,40 @@ constexpr int kThreads = (kComputeWarps + 2) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kHalf = kTile / 2;                    // columns handled by one compute thread
 
-enum BwdBar { B_XFULL = 0, B_YFULL0, B_YFULL1, B_YEMPTY0, B_YEMPTY1, B_SFULL0, B_SFULL1, B_DPFULL, B_PFULL0, B_PFULL1, B_DSFULL, B_ACCFULL, B_CFULL, B_COUNT };
+// ---------------------------------------------------------------------------------------
+// dK/dV kernel (kv-outer).  TMEM is full (T1 | T2 | dV | dK), so there is one score buffer:
+//     T1(0) T2(0) | dV(0), T1(1) | dK(0), T2(1) | dV(1), T1(2) | ...
+// P(i) is written over S(i) in T1 and dS(i) over dP(i) in T2.  LSE2 and delta are per
+// column here (one query per column): the producer warp brings the 128 values of each into
+// shared memory with two 512-byte bulk copies per item, on the same barrier as the Q and dO
+// tiles (plus segment ids and positions for partial tiles), so the register math never
+// waits on a global load.  A tile that crosses the end of the sequence, or rows that are
+// not 16-byte aligned, are copied by the producer's lanes instead.
+// Shared memory: K, V 2 x 32 KB + 2 stages x (Q, dO 64 KB + column info 2 KB).
+// ---------------------------------------------------------------------------------------
+enum KvBar { K_XFULL = 0, K_YFULL0, K_YFULL1, K_YEMPTY0, K_YEMPTY1, K_SFULL0, K_SFULL1, K_DPFULL, K_PFULL0, K_PFULL1, K_DSFULL, K_ACCFULL, K_COUNT };
 
 template <int D>
-struct BwdSmem {
+struct KvSmem {
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kBoxBytes = kTile * 64 * 2;
   static constexpr int kX1 = 0, kX2 = kTileBytes;
-  static constexpr int kY = 2 * kTileBytes;              // stage s: Y1 at kY + s*2*tile, Y2 right after
-  static constexpr int kCols = 6 * kTileBytes;           // per-column info, 3 buffers x 4 arrays x 128 x 4 B
-  static constexpr int kBars = kCols + 3 * 4 * kTile * 4;
-  static constexpr int kTmemSlot = kBars + 8 * B_COUNT;
+  static constexpr int kY = 2 * kTileBytes;              // stage s: Q at kY + s*2*tile, dO right after
+  static constexpr int kCols = 6 * kTileBytes;           // stage s: seg | pos | lse2 | delta, 128 x 4 B each
+  static constexpr int kColBytes = kTile * 4;
+  static constexpr int kBars = kCols + 2 * 4 * kColBytes;
+  static constexpr int kTmemSlot = kBars + 8 * K_COUNT;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4 + 1024;
+  static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
-// Compute thread layout: thread t of the 256 owns outer row (t % 128) = TMEM lane, and the
-// column half (t / 128) of every 128-column tile.  P and dS (bf16 pairs) of half h are
-// written back at column offset 64*h of the T1 / T2 regions, i.e. inside the fp32 columns
-// that same thread has already read, so the two halves never touch each other's columns.
-template <int D, bool kKvOuter>
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_constant__ CUtensorMap tmap_x2,
-                const __grid_constant__ CUtensorMap tmap_y1, const __grid_constant__ CUtensorMap tmap_y2,
-                const BwdArgs a) {
-  using L = BwdSmem<D>;
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                     const BwdArgs a) {
+  using L = KvSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -73,44 +79,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   int* s_cols = reinterpret_cast<int*>(smem + L::kCols);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int row_rank, xh;                          // xh: query head (dQ kernel) or kv head (dK/dV kernel)
-  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, kKvOuter ? a.kv_heads : a.q_heads, &row_rank, &xh);
+  int row_rank, kvh;
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.kv_heads, &row_rank, &kvh);
   const long long list_row = __ldg(a.list.order + row_rank);     // longest lists first
-  const int b = int(list_row / a.list.n_outer_tiles), ot = int(list_row % a.list.n_outer_tiles);
+  const int b = int(list_row / a.list.n_outer_tiles), kt = int(list_row % a.list.n_outer_tiles);
   const int group = a.group;
   const int count = __ldg(a.list.counts + list_row);
   const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
-  const int n_items = kKvOuter ? count * group : count;
-  const int outer_len = kKvOuter ? a.tok.kv_len : a.tok.q_len;
-  const int inner_len = kKvOuter ? a.tok.q_len : a.tok.kv_len;
+  const int n_items = count * group;           // item i: query head kvh*group + i / count, query tile list[i % count]
+  const int q_len = a.tok.q_len;
 
-  const int row = tid & (kTile - 1);         // outer row / TMEM lane of a compute thread
-  const int half = (tid >> 7) & 1;           // column half of a compute thread
-  const int r = ot * kTile + row;
+  const int row = tid & (kTile - 1);           // kv row / TMEM lane of a compute thread
+  const int half = (tid >> 7) & 1;             // column half of a compute thread
+  const int r = kt * kTile + row;
   const bool is_compute = tid < kComputeThreads;
-  const bool row_valid = is_compute && (r < outer_len);
+  const bool row_valid = is_compute && (r < a.tok.kv_len);
+  float* dk_row = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
+  float* dv_row = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
 
-  if (n_items == 0) {                        // no contributing tile: zero gradients
+  if (n_items == 0) {                          // no contributing tile: zero gradients
     if (row_valid) {
-      if (kKvOuter) {
-        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4* dk = reinterpret_cast<float4*>(a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D) + half * (D / 8);
-        float4* dv = reinterpret_cast<float4*>(a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D) + half * (D / 8);
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) { dk[i] = z; dv[i] = z; }
-      } else {
-        uint4 z = make_uint4(0, 0, 0, 0);
-        uint4* dq = reinterpret_cast<uint4*>(a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2]) + half * (D / 16);
-#pragma unroll
-        for (int i = 0; i < D / 16; ++i) dq[i] = z;
-      }
+      for (int i = 0; i < D / 8; ++i) { reinterpret_cast<float4*>(dk_row)[i] = z; reinterpret_cast<float4*>(dv_row)[i] = z; }
     }
     return;
   }
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(&bars[i], (i == B_PFULL0 || i == B_PFULL1 || i == B_DSFULL || i == B_CFULL) ? kComputeThreads : 1);
+    for (int i = 0; i < K_COUNT; ++i)
+      mbar_init(&bars[i], (i == K_PFULL0 || i == K_PFULL1 || i == K_DSFULL) ? kComputeThreads : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -123,37 +121,93 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   const uint32_t tAcc1 = tmem_base + 2 * kTile, tAcc2 = tmem_base + 3 * kTile;
 
   if (warp == kProducerWarp) {
-    // ------------------------------------------------------------------ producer
-    if (lane == 0) {
-      prefetch_tmap(&tmap_x1); prefetch_tmap(&tmap_x2); prefetch_tmap(&tmap_y1); prefetch_tmap(&tmap_y2);
-      mbar_arrive_expect_tx(&bars[B_XFULL], 2 * L::kTileBytes);
+    // ------------------------------------------------------------------ producer (whole warp; one elected lane issues)
+    const int n = __shfl_sync(0xffffffffu, n_items, 0);
+    const int cnt = __shfl_sync(0xffffffffu, count, 0);
+    if (elect_one()) {
+      prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do);
+      mbar_arrive_expect_tx(&bars[K_XFULL], 2 * L::kTileBytes);
 #pragma unroll
       for (int x = 0; x < D / 64; ++x) {
-        tma_load_4d(smem + L::kX1 + x * L::kBoxBytes, &tmap_x1, &bars[B_XFULL], x * 64, xh, ot * kTile, b);
-        tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_x2, &bars[B_XFULL], x * 64, xh, ot * kTile, b);
+        tma_load_4d(smem + L::kX1 + x * L::kBoxBytes, &tmap_k, &bars[K_XFULL], x * 64, kvh, kt * kTile, b);
+        tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_v, &bars[K_XFULL], x * 64, kvh, kt * kTile, b);
       }
-      bool ok = true;
-      uint32_t e_next = __ldg(list);               // list entries are fetched one iteration ahead
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i & 1;
-        const int yh = kKvOuter ? (xh * group + i / count) : (xh / group);
-        const int u = int(e_next & ~kPartialBit);
-        if (i + 1 < n_items) e_next = __ldg(list + (kKvOuter ? ((i + 1) % count) : (i + 1)));
-        if (i >= 2) ok = mbar_wait(&bars[B_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, B_YEMPTY0 + st);
-        if (!ok) break;
-        uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
-        uint8_t* y2 = y1 + L::kTileBytes;
-        mbar_arrive_expect_tx(&bars[B_YFULL0 + st], 2 * L::kTileBytes);
+    }
+    __syncwarp();
+    bool ok = true;
+    uint32_t e_next = __ldg(list);                 // list entries are fetched one iteration ahead
+    int li = 0, qh = kvh * group;                  // index into the list, query head
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i & 1;
+      const uint32_t e = e_next;
+      const int u = int(e & ~kPartialBit);
+      const bool partial = (e & kPartialBit) != 0;
+      const int yh = qh;
+      if (++li == cnt) { li = 0; ++qh; }
+      if (i + 1 < n) e_next = __ldg(list + li);
+      if (i >= 2) {
+        ok = mbar_wait(&bars[K_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, K_YEMPTY0 + st);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (!ok) break;
+      uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
+      uint8_t* y2 = y1 + L::kTileBytes;
+      int* cs = s_cols + st * 4 * kTile;
+      const int col0 = u * kTile;
+      const float* lse_src = a.lse + ((long long)b * a.q_heads + yh) * q_len + col0;
+      const float* dl_src = a.delta + ((long long)b * a.q_heads + yh) * q_len + col0;
+      const int32_t* seg_src = a.tok.q_seg + (long long)b * q_len + col0;
+      const int32_t* pos_src = a.tok.sequential ? nullptr : a.tok.q_pos + (long long)b * q_len + col0;
+      uintptr_t align = reinterpret_cast<uintptr_t>(lse_src) | reinterpret_cast<uintptr_t>(dl_src);
+      if (partial) align |= reinterpret_cast<uintptr_t>(seg_src) | reinterpret_cast<uintptr_t>(pos_src);
+      const bool bulk = (col0 + kTile <= q_len) && ((align & 15) == 0);
+      uint32_t extra = 0;
+      if (bulk) {
+        extra = 2 * L::kColBytes;
+        if (partial) {
+          extra += L::kColBytes;
+          if (pos_src) {
+            extra += L::kColBytes;
+          } else {
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x) {
-          tma_load_4d(y1 + x * L::kBoxBytes, &tmap_y1, &bars[B_YFULL0 + st], x * 64, yh, u * kTile, b);
-          tma_load_4d(y2 + x * L::kBoxBytes, &tmap_y2, &bars[B_YFULL0 + st], x * 64, yh, u * kTile, b);
+            for (int k = 0; k < kTile / 32; ++k) cs[kTile + lane + 32 * k] = query_position(a.tok, b, col0 + lane + 32 * k);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < kTile / 32; ++k) {
+          const int j = lane + 32 * k;
+          const bool valid = col0 + j < q_len;
+          reinterpret_cast<float*>(cs)[2 * kTile + j] = valid ? __ldg(lse_src + j) : INFINITY;   // exp2(-inf) = 0
+          reinterpret_cast<float*>(cs)[3 * kTile + j] = valid ? __ldg(dl_src + j) : 0.f;
+          if (partial) {
+            cs[j] = valid ? __ldg(seg_src + j) : KVAX_B200_PADDING_SEGMENT_ID;
+            cs[kTile + j] = valid ? query_position(a.tok, b, col0 + j) : 0;
+          }
         }
       }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&bars[K_YFULL0 + st], 2 * L::kTileBytes + extra);
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x) {
+          tma_load_4d(y1 + x * L::kBoxBytes, &tmap_q, &bars[K_YFULL0 + st], x * 64, yh, u * kTile, b);
+          tma_load_4d(y2 + x * L::kBoxBytes, &tmap_do, &bars[K_YFULL0 + st], x * 64, yh, u * kTile, b);
+        }
+        if (bulk) {
+          bulk_load_1d(cs + 2 * kTile, lse_src, L::kColBytes, &bars[K_YFULL0 + st]);
+          bulk_load_1d(cs + 3 * kTile, dl_src, L::kColBytes, &bars[K_YFULL0 + st]);
+          if (partial) {
+            bulk_load_1d(cs, seg_src, L::kColBytes, &bars[K_YFULL0 + st]);
+            if (pos_src) bulk_load_1d(cs + kTile, pos_src, L::kColBytes, &bars[K_YFULL0 + st]);
+          }
+        }
+      }
+      __syncwarp();
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    static_assert(kKvOuter, "the query-outer pass has a kernel of its own");
     constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
     constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
     const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
@@ -180,47 +234,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
       for (int kk = 0; kk < kTile / 16; ++kk)
         umma_ts_lo(acc_addr, a_addr + (kk >> 2) * kHalf + (kk & 3) * 8, y_lo + ((kk * 16 * 128) >> 4), idesc_acc, acc_on | (kk > 0));
     };
-    wait(B_XFULL, 0, false);
-    if (ok) wait(B_YFULL0, 0, false);
+    wait(K_XFULL, 0, false);
+    if (ok) wait(K_YFULL0, 0, false);
     if (ok) {
       if (elect_one()) {
         issue_t(tT1, x1_lo, sdesc_lo_sw128(ybase, 16));
-        umma_commit(&bars[B_SFULL0]);
+        umma_commit(&bars[K_SFULL0]);
         issue_t(tT2, x2_lo, sdesc_lo_sw128(ybase + L::kTileBytes, 16));
-        umma_commit(&bars[B_DPFULL]);
+        umma_commit(&bars[K_DPFULL]);
       }
       __syncwarp();
     }
-    // TMEM is full (T1 | T2 | dV | dK), so there is one score buffer:  ... | dV(i), T1(i+1) | dK(i), T2(i+1) | ...
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
       const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
       const uint32_t acc_on = (i > 0) ? 1u : 0u;
       const bool more = (i + 1 < n);
-      wait(B_PFULL0 + st, (i >> 1) & 1, true);                                      // P(i) written, S(i) consumed
+      wait(K_PFULL0 + st, (i >> 1) & 1, true);                                      // P(i) written, S(i) consumed
       if (!ok) break;
       if (elect_one()) issue_acc(tAcc1, tT1, sdesc_lo_sw128(y2, L::kBoxBytes), acc_on);   // dV += P^T dO
       __syncwarp();
       if (more) {
-        wait(B_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
+        wait(K_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
         if (!ok) break;
         if (elect_one()) {
           issue_t(tT1, x1_lo, sdesc_lo_sw128(y1n, 16));                             // scores of item i+1
-          umma_commit(&bars[B_SFULL0 + (st ^ 1)]);
+          umma_commit(&bars[K_SFULL0 + (st ^ 1)]);
         }
         __syncwarp();
       }
-      wait(B_DSFULL, i & 1, true);                                                  // dS(i) written
+      wait(K_DSFULL, i & 1, true);                                                  // dS(i) written
       if (!ok) break;
       if (elect_one()) {
         issue_acc(tAcc2, tT2, sdesc_lo_sw128(y1, L::kBoxBytes), acc_on);            // dK += dS^T Q
-        umma_commit(&bars[B_YEMPTY0 + st]);
+        umma_commit(&bars[K_YEMPTY0 + st]);
         if (more) {
           issue_t(tT2, x2_lo, sdesc_lo_sw128(y2n, 16));                             // dP of item i+1
-          umma_commit(&bars[B_DPFULL]);
+          umma_commit(&bars[K_DPFULL]);
         } else {
-          umma_commit(&bars[B_ACCFULL]);
+          umma_commit(&bars[K_ACCFULL]);
         }
       }
       __syncwarp();
@@ -228,101 +281,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
   } else {
     // ------------------------------------------------------------------ register math
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t my_t1_even = tT1 + lane_base + half * kHalf;   // fp32 columns of this thread; P goes to the first 32 of them
-    const uint32_t my_t1_odd = (kKvOuter ? tT1 : tAcc1) + lane_base + half * kHalf;   // dQ kernel: second score buffer
-    const uint32_t my_t2 = tT2 + lane_base + half * kHalf;
+    const int cb = half * kHalf;                              // first column (within the tile) of this thread
+    const uint32_t my_t1 = tT1 + lane_base + cb;              // fp32 columns of this thread; P goes to the first 32 of them
+    const uint32_t my_t2 = tT2 + lane_base + cb;
     const float c = a.scale_log2e;
-    const RowBounds rb = load_bounds(a.mask, b, min(r, outer_len - 1));
-    int o_seg = KVAX_B200_PADDING_SEGMENT_ID, o_pos = 0;
-    float row_neg_lse = 0.f, row_delta = 0.f;
+    const RowBounds rb = load_bounds(a.mask, b, min(r, a.tok.kv_len - 1));
+    int kv_seg = KVAX_B200_PADDING_SEGMENT_ID, kv_pos = 0;
     if (row_valid) {
-      if (kKvOuter) {
-        o_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
-        o_pos = a.tok.sequential ? r : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + r);
-      } else {
-        o_seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + r);
-        o_pos = query_position(a.tok, b, r);
-        row_neg_lse = -__ldg(a.lse + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
-        row_delta = __ldg(a.delta + ((long long)b * a.q_heads + xh) * a.tok.q_len + r);
-      }
+      kv_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
+      kv_pos = a.tok.sequential ? r : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + r);
     }
     bool ok = true;
-    // Per-column info of inner tile `i` (one column per thread of the first half): segment id
-    // and position (partial tiles only) and, for the dK/dV kernel, -LSE2 and delta of the query
-    // rows.  Fetched from global memory one iteration ahead so that the L2 latency is hidden.
-    struct ColInfo { int seg, pos; float nlse, dl; };
-    auto load_cols = [&](int i, uint32_t e) {
-      ColInfo ci{KVAX_B200_PADDING_SEGMENT_ID, 0, -INFINITY, 0.f};
-      const bool partial = (e & kPartialBit) != 0;
-      if ((kKvOuter || partial) && half == 0) {
-        const int col = int(e & ~kPartialBit) * kTile + row;
-        if (col < inner_len) {
-          if (kKvOuter) {
-            const int yh = xh * group + i / count;
-            const long long o = ((long long)b * a.q_heads + yh) * a.tok.q_len + col;
-            ci.nlse = -__ldg(a.lse + o); ci.dl = __ldg(a.delta + o);
-            if (partial) { ci.seg = __ldg(a.tok.q_seg + (long long)b * a.tok.q_len + col); ci.pos = query_position(a.tok, b, col); }
-          } else {
-            ci.seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + col);
-            ci.pos = a.tok.sequential ? col : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + col);
-          }
-        }
-      }
-      return ci;
-    };
-    // Staging protocol: the info of item i+1 is written to buffer (i+1) % 3 at the start of
-    // iteration i and announced on C_FULL right away, so the wait at the start of iteration
-    // i+1 normally finds it complete.  A buffer is rewritten three items later; every thread
-    // has then passed the C_FULL phase that follows its last read of it.
-    auto stage_cols = [&](int i, uint32_t e, const ColInfo& ci) {
-      if ((kKvOuter || (e & kPartialBit)) && half == 0) {
-        int* cs = s_cols + (i % 3) * 4 * kTile;
-        cs[row] = ci.seg; cs[kTile + row] = ci.pos;
-        cs[2 * kTile + row] = __float_as_int(ci.nlse); cs[3 * kTile + row] = __float_as_int(ci.dl);
-      }
-      mbar_arrive(&bars[B_CFULL]);
-    };
-    auto list_at = [&](int i) { return __ldg(list + (kKvOuter ? (i % count) : i)); };
-    uint32_t e_cur = list_at(0);
-    stage_cols(0, e_cur, load_cols(0, e_cur));
-    uint32_t e_next = (n_items > 1) ? list_at(1) : 0u;       // entry i+1
-    ColInfo ci_next = (n_items > 1) ? load_cols(1, e_next) : ColInfo{KVAX_B200_PADDING_SEGMENT_ID, 0, -INFINITY, 0.f};
-    uint32_t e_next2 = (n_items > 2) ? list_at(2) : 0u;      // entry i+2
+    uint32_t e_next = __ldg(list);
+    int li = 0;
     for (int i = 0; i < n_items && ok; ++i) {
-      const uint32_t e = e_cur;
+      const uint32_t e = e_next;
+      if (++li == count) li = 0;
+      if (i + 1 < n_items) e_next = __ldg(list + li);
       const int c0 = int(e & ~kPartialBit) * kTile;
       const bool partial = (e & kPartialBit) != 0;
-      const int sbuf = i & 1;                                 // score buffer / barrier pair of this item
-      int* cs = s_cols + (i % 3) * 4 * kTile;
-      ok = mbar_wait(&bars[B_CFULL], i & 1, abort_flag, a.status, B_CFULL);
-      if (!ok) break;
-      if (i + 1 < n_items) {
-        stage_cols(i + 1, e_next, ci_next);
-        e_cur = e_next;
-        if (i + 2 < n_items) {                      // request the info of item i+2 now
-          e_next = e_next2;
-          ci_next = load_cols(i + 2, e_next);
-          if (i + 3 < n_items) e_next2 = list_at(i + 3);
-        }
-      }
-      const int cb = half * kHalf;            // first column (within the tile) of this thread
-      const float4* cs_nlse = reinterpret_cast<const float4*>(cs + 2 * kTile + cb);
+      const int st = i & 1;                                   // Y stage, column-info buffer and barrier pair of this item
+      const int* cs = s_cols + st * 4 * kTile;
+      const float4* cs_lse = reinterpret_cast<const float4*>(cs + 2 * kTile + cb);
       const float4* cs_dl = reinterpret_cast<const float4*>(cs + 3 * kTile + cb);
+
+      // column info of this item has landed together with its Q and dO tiles
+      ok = mbar_wait(&bars[K_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, K_YFULL0 + st);
+      if (!ok) break;
 
       // element mask of partial tiles, one bit per column of this thread's half
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (partial) {
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
-          keep[ch] = keep_bits32<kKvOuter>(rb, c0 + cb + ch * 32, inner_len, row_valid, o_seg, o_pos, cs + cb + ch * 32,
-                                           cs + kTile + cb + ch * 32);
+          keep[ch] = keep_bits32<true>(rb, c0 + cb + ch * 32, q_len, row_valid, kv_seg, kv_pos, cs + cb + ch * 32, cs + kTile + cb + ch * 32);
       }
 
       // ---- P = exp2(S * scale*log2e - LSE2): the 64 values of this thread stay in registers
-      ok = mbar_wait(&bars[B_SFULL0 + sbuf], (i >> 1) & 1, abort_flag, a.status, B_SFULL0 + sbuf);
+      ok = mbar_wait(&bars[K_SFULL0 + st], (i >> 1) & 1, abort_flag, a.status, K_SFULL0 + st);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t my_t1 = sbuf ? my_t1_odd : my_t1_even;
       uint32_t v[2][32];
       tmem_ld32(my_t1, v[0]);
       tmem_ld32(my_t1 + 32, v[1]);
@@ -331,29 +329,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
         tmem_ld_wait(v[ch]);
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 4) {
-          float4 nl = make_float4(row_neg_lse, row_neg_lse, row_neg_lse, row_neg_lse);
-          if (kKvOuter) nl = cs_nlse[(ch * 32 + jj) >> 2];
-          const float n4[4] = {nl.x, nl.y, nl.z, nl.w};
+          const float4 ls = cs_lse[(ch * 32 + jj) >> 2];
+          const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
-            float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj + t]), c, n4[t]));
+            float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj + t]), c, -l4[t]));
             if (partial) pv = ((keep[ch] >> (jj + t)) & 1u) ? pv : 0.f;
             v[ch][jj + t] = __float_as_uint(pv);
           }
         }
-        if (kKvOuter) {
-          uint32_t pk[16];
+        uint32_t pk[16];
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
-          tmem_st16(my_t1 + ch * 16, pk);
-        }
+        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
+        tmem_st16(my_t1 + ch * 16, pk);
       }
-      if (kKvOuter) tmem_st_wait();
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars[B_PFULL0 + sbuf]);
+      mbar_arrive(&bars[K_PFULL0 + st]);
 
       // ---- dS = P * (dP - delta)
-      ok = mbar_wait(&bars[B_DPFULL], i & 1, abort_flag, a.status, B_DPFULL);
+      ok = mbar_wait(&bars[K_DPFULL], i & 1, abort_flag, a.status, K_DPFULL);
       if (!ok) break;
       tc_fence_after();
       uint32_t dp[2][32];
@@ -362,70 +357,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x1, const __grid_consta
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         tmem_ld_wait(dp[ch]);
-        uint32_t dk[16];
+        uint32_t ds[16];
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 4) {
-          float4 dl = make_float4(row_delta, row_delta, row_delta, row_delta);
-          if (kKvOuter) dl = cs_dl[(ch * 32 + jj) >> 2];
+          const float4 dl = cs_dl[(ch * 32 + jj) >> 2];
           const float d0 = __uint_as_float(v[ch][jj + 0]) * (__uint_as_float(dp[ch][jj + 0]) - dl.x);
           const float d1 = __uint_as_float(v[ch][jj + 1]) * (__uint_as_float(dp[ch][jj + 1]) - dl.y);
           const float d2 = __uint_as_float(v[ch][jj + 2]) * (__uint_as_float(dp[ch][jj + 2]) - dl.z);
           const float d3 = __uint_as_float(v[ch][jj + 3]) * (__uint_as_float(dp[ch][jj + 3]) - dl.w);
-          dk[jj >> 1] = pack_bf16(d0, d1);
-          dk[(jj >> 1) + 1] = pack_bf16(d2, d3);
+          ds[jj >> 1] = pack_bf16(d0, d1);
+          ds[(jj >> 1) + 1] = pack_bf16(d2, d3);
         }
         // both 32-column chunks were loaded before the first store, so writing over the
         // first 32 columns is safe
-        tmem_st16(my_t2 + ch * 16, dk);
+        tmem_st16(my_t2 + ch * 16, ds);
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars[B_DSFULL]);
+      mbar_arrive(&bars[K_DSFULL]);
     }
 
-    if (ok) ok = mbar_wait(&bars[B_ACCFULL], 0, abort_flag, a.status, B_ACCFULL);
+    if (ok) ok = mbar_wait(&bars[K_ACCFULL], 0, abort_flag, a.status, K_ACCFULL);
     if (ok) {
       tc_fence_after();
       // each thread stores D/2 columns of its row: columns [half*D/2, (half+1)*D/2)
-      constexpr int kCh = D / 64;             // 32-column chunks per thread
-      if (kKvOuter) {
-        float* dk = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D + half * (D / 2);
-        float* dv = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + xh) * D + half * (D / 2);
 #pragma unroll
-        for (int ch = 0; ch < kCh; ++ch) {
-          uint32_t v1[32], v2[32];
-          tmem_ld32(tAcc1 + lane_base + half * (D / 2) + ch * 32, v1);
-          tmem_ld32(tAcc2 + lane_base + half * (D / 2) + ch * 32, v2);
-          tmem_ld_wait(v1);
-          tmem_ld_wait(v2);
-          if (row_valid) {
+      for (int ch = 0; ch < D / 64; ++ch) {
+        uint32_t v1[32], v2[32];
+        tmem_ld32(tAcc1 + lane_base + half * (D / 2) + ch * 32, v1);
+        tmem_ld32(tAcc2 + lane_base + half * (D / 2) + ch * 32, v2);
+        tmem_ld_wait(v1);
+        tmem_ld_wait(v2);
+        if (row_valid) {
 #pragma unroll
-            for (int jj = 0; jj < 32; jj += 4) {
-              reinterpret_cast<float4*>(dv)[(ch * 32 + jj) >> 2] =
-                  make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
-              reinterpret_cast<float4*>(dk)[(ch * 32 + jj) >> 2] =
-                  make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
-                              __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
-            }
-          }
-        }
-      } else {
-        __nv_bfloat16* dq = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)xh * a.q_strides[2] + half * (D / 2);
-#pragma unroll
-        for (int ch = 0; ch < kCh; ++ch) {
-          uint32_t v[32];
-          tmem_ld32(tAcc2 + lane_base + half * (D / 2) + ch * 32, v);
-          tmem_ld_wait(v);
-          if (row_valid) {
-#pragma unroll
-            for (int jj = 0; jj < 32; jj += 8) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(v[jj + 0]) * a.scale, __uint_as_float(v[jj + 1]) * a.scale);
-              w.y = pack_bf16(__uint_as_float(v[jj + 2]) * a.scale, __uint_as_float(v[jj + 3]) * a.scale);
-              w.z = pack_bf16(__uint_as_float(v[jj + 4]) * a.scale, __uint_as_float(v[jj + 5]) * a.scale);
-              w.w = pack_bf16(__uint_as_float(v[jj + 6]) * a.scale, __uint_as_float(v[jj + 7]) * a.scale);
-              reinterpret_cast<uint4*>(dq)[(ch * 32 + jj) >> 3] = w;
-            }
+          for (int jj = 0; jj < 32; jj += 4) {
+            reinterpret_cast<float4*>(dv_row)[(ch * 32 + jj) >> 2] =
+                make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
+            reinterpret_cast<float4*>(dk_row)[(ch * 32 + jj) >> 2] =
+                make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
+                            __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
           }
         }
       }
@@ -770,16 +740,15 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
   }
 }
 
-template <int D, bool kKvOuter>
-int launch_bwd(const BwdLaunch& L, cudaStream_t stream) {
-  constexpr int smem = BwdSmem<D>::kTotal;
-  auto kern = attn_bwd_kernel<D, kKvOuter>;
+template <int D>
+int launch_dkdv(const BwdLaunch& L, cudaStream_t stream) {
+  constexpr int smem = KvSmem<D>::kTotal;
+  auto kern = attn_bwd_dkdv_kernel<D>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
-  dim3 grid(L.args.list.n_outer_tiles * L.batch * (kKvOuter ? L.args.kv_heads : L.args.q_heads), 1, 1);
-  kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);
+  dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // K, V, Q, dO
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
-
 
 template <int D>
 int launch_dq(const BwdLaunch& L, cudaStream_t stream) {
@@ -794,8 +763,8 @@ int launch_dq(const BwdLaunch& L, cudaStream_t stream) {
 }  // namespace
 
 int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream) {
-  if (L.head_dim == 128) return kv_outer ? launch_bwd<128, true>(L, stream) : launch_dq<128>(L, stream);
-  if (L.head_dim == 64) return kv_outer ? launch_bwd<64, true>(L, stream) : launch_dq<64>(L, stream);
+  if (L.head_dim == 128) return kv_outer ? launch_dkdv<128>(L, stream) : launch_dq<128>(L, stream);
+  if (L.head_dim == 64) return kv_outer ? launch_dkdv<64>(L, stream) : launch_dq<64>(L, stream);
   return KVAX_B200_EUNSUPPORTED;
 }
 
