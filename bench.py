@@ -197,6 +197,8 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--cp-mode", default="auto", choices=("auto", "all_gather", "head_exchange"),
+                    help="context-parallel schedule for --gpus N > 1")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kvax_b200", choices=["kvax_b200", "reference"])
@@ -239,6 +241,8 @@ def main():
     flops_fwd = gen.attention_flops(n_tiles, Hq, D, D)
     flops_step = 3.5 * flops_fwd
 
+    kv.set_context_parallel_mode(args.cp_mode)
+    hx = cp > 1 and Hkv % cp == 0 and args.cp_mode != "all_gather"
     mesh = kv.Mesh(("data", "context"), (1, cp))
     q_spec = ("data", "context" if cp > 1 else None, None, None)
     kv_spec = ("data", None, None, None)
@@ -395,13 +399,14 @@ def main():
         return
 
     value = flops_step / (ms_step * 1e-3) / 1e12
-    kernels_per_step = 2 + (2 + 1) + (2 + 1 + 2) + (0 if cp == 1 else 6)   # mask(2) fwd(sched+attn) bwd(2 sched, delta, dq, dkdv) [+ permutes]
+    # mask(2) fwd(sched+attn) bwd(2 sched, delta, dq, dkdv) [+ token permutes; the head exchange rebuilds the masks]
+    kernels_per_step = 2 + (2 + 1) + (2 + 1 + 2) + (0 if cp == 1 else (12 if hx else 6))
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": cp, "steps": K, "warmup": W,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": cfg.name, "batch": B, "seq_len": S, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D,
-                   "tile": TILE, "parallelism": f"cp{cp}", "unmasked_tile_pairs": n_tiles,
+                   "tile": TILE, "parallelism": f"cp{cp}" + ((":head_exchange" if hx else ":all_gather") if cp > 1 else ""), "unmasked_tile_pairs": n_tiles,
                    "flops_per_step": flops_step, "cache": "inputs larger than L2 (Q alone exceeds 126 MB)",
                    "positions": "restart at 0 in every document", "step": "3 block masks + forward + backward"},
         "tokens_per_s": B * S / (ms_step * 1e-3),

@@ -6,7 +6,7 @@ __version__ = ".".join(str(v) for v in __version_info__)
 
 import kvax_b200.ops as ops
 import kvax_b200.utils as utils
-from kvax_b200.ops import create_attention_mask, flash_attention
+from kvax_b200.ops import create_attention_mask, flash_attention, get_context_parallel_mode, set_context_parallel_mode
 from kvax_b200.utils import (
     PADDING_SEGMENT_ID,
     FlashAttentionParamsConfig,

@@ -8,11 +8,24 @@ directly through strided TMA descriptors, so the four layout transposes of the r
 Execution model: one process per GPU.  With context parallelism (the query sequence
 axis of `query_specs` names a mesh axis of size > 1) every process passes its own slice
 of the permuted sequence for query, key and value — what a device sees of the
-reference's global arrays — and the full, un-permuted kv positions / segment ids.  The
-op all-gathers K and V over NCCL into natural order, runs the kernels on the local
-queries, and in the backward pass reduce-scatters fp32 dK/dV back to their owners before
-casting to the input dtype (the reference keeps fp32 through that reduction,
-flash_attention_triton.py:2107-2115).
+reference's global arrays — and the full, un-permuted kv positions / segment ids.
+
+Two context-parallel schedules produce the same results:
+
+* "all_gather" (the reference's, flash_attention_triton.py:2064-2115): K and V are
+  all-gathered over NCCL into natural order, the kernels run on the local queries, and the
+  backward pass reduce-scatters fp32 dK/dV back to their owners before the cast to the
+  input dtype.  Under document masks the work per rank is uneven, because the
+  load-balancing permutation only balances a plain causal mask.
+* "head_exchange": an all-to-all turns the sequence sharding into a head sharding
+  (every rank receives the whole sequence for heads/CP of the heads), the kernels run the
+  single-device problem in natural token order on those heads, and a second all-to-all
+  brings the output (and, in the backward pass, dQ/dK/dV) back to sequence sharding.  The
+  work per rank is exactly 1/CP of the whole, whatever the mask, and no gradient reduction
+  is needed: every dK/dV element is complete on one rank.  It needs kv_heads % CP == 0.
+
+`set_context_parallel_mode("auto")` (the default) picks "head_exchange" when the head
+counts allow it.
 """
 from __future__ import annotations
 
@@ -24,6 +37,22 @@ from kvax_b200 import _lib
 from kvax_b200.utils.common import FlashAttentionParamsConfig, get_default_flash_attention_params
 from kvax_b200.utils.sharding import Mesh, _check_mesh_or_get_global, get_query_context_mesh_axis_name
 from kvax_b200.utils.typing import AttentionMask
+
+_CP_MODES = ("auto", "all_gather", "head_exchange")
+_cp_mode = "auto"
+
+
+def set_context_parallel_mode(mode: str) -> None:
+    """Chooses the context-parallel schedule: "auto", "all_gather" or "head_exchange"."""
+    global _cp_mode
+    if mode not in _CP_MODES:
+        raise ValueError(f"unknown context-parallel mode {mode!r}; expected one of {_CP_MODES}")
+    _cp_mode = mode
+
+
+def get_context_parallel_mode() -> str:
+    return _cp_mode
+
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 192, 256)   # what the reference accepts
 _KERNEL_HEAD_DIMS = (64, 128)                         # what the sm_100a kernels cover today
@@ -179,6 +208,50 @@ def _scatter_dkv(g: torch.Tensor, cp: int, group, permuted: bool, out_dtype, per
     return local.to(out_dtype)
 
 
+def _seq_to_heads(x: torch.Tensor, cp: int, group, permuted: bool, permute_fn=None) -> torch.Tensor:
+    """All-to-all from sequence sharding to head sharding: local (B, S_loc, H, D) of every
+    rank -> (B, S, H / cp, D) in natural token order; rank j receives heads
+    [j * H / cp, (j + 1) * H / cp)."""
+    import torch.distributed as dist
+    from kvax_b200.utils.permutation import _permute_one
+    _permute_one = permute_fn or _permute_one
+
+    B, Sl, H = x.shape[:3]
+    tail = tuple(x.shape[3:])
+    Hl = H // cp
+    send = x.reshape(B, Sl, cp, Hl, *tail).permute(2, 0, 1, 3, *range(4, 4 + len(tail))).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)             # recv[j]: tokens of rank j
+    if B == 1:
+        full = recv.view(1, cp * Sl, Hl, *tail)
+    else:
+        full = recv.transpose(0, 1).contiguous().view(B, cp * Sl, Hl, *tail)
+    return _permute_one(full, cp, reverse=True) if permuted else full
+
+
+def _heads_to_seq(y: torch.Tensor, cp: int, group, permuted: bool, permute_fn=None) -> torch.Tensor:
+    """Inverse of `_seq_to_heads`: (B, S, H / cp, D) in natural order on every rank ->
+    the local (B, S / cp, H, D) slice of the (permuted) sequence."""
+    import torch.distributed as dist
+    from kvax_b200.utils.permutation import _permute_one
+    _permute_one = permute_fn or _permute_one
+
+    B, S, Hl = y.shape[:3]
+    tail = tuple(y.shape[3:])
+    Sl = S // cp
+    if permuted:
+        y = _permute_one(y.contiguous(), cp, reverse=False)
+    send = y.reshape(B, cp, Sl, Hl, *tail).transpose(0, 1).contiguous()   # send[j]: tokens of rank j
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)             # recv[j]: heads of rank j
+    return recv.permute(1, 2, 0, 3, *range(4, 4 + len(tail))).reshape(B, Sl, cp * Hl, *tail)
+
+
+def _gather_tokens(x: torch.Tensor, cp: int, group, permuted: bool, permute_fn=None) -> torch.Tensor:
+    """All-gather of per-token (B, S_loc) arrays into (B, S) in natural order."""
+    return _gather_kv(x.unsqueeze(-1).unsqueeze(-1), cp, group, permuted, permute_fn)[:, :, 0, 0].contiguous()
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, masks, scale, fwd_params, bwd_params,
@@ -219,6 +292,58 @@ class _FlashAttention(torch.autograd.Function):
         else:
             dk, dv = dk.to(kv_dtype), dv.to(kv_dtype)
         return (dq, dk, dv) + (None,) * 13
+
+
+class _FlashAttentionHeadExchange(torch.autograd.Function):
+    """Context parallelism by head exchange (see the module docstring).  The masks of the
+    single-device problem are rebuilt from the gathered positions and segment ids with the
+    same bit-exact mask builder; the per-rank masks the caller passed are not used."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, n_masks, scale, fwd_params, bwd_params,
+                sequential, permuted, cp, group):
+        from kvax_b200.ops.mask_creator import build_masks
+
+        q_h = _seq_to_heads(query, cp, group, permuted)
+        k_h = _seq_to_heads(key, cp, group, permuted)
+        v_h = _seq_to_heads(value, cp, group, permuted)
+        q_pos_f = _gather_tokens(q_pos, cp, group, permuted)
+        q_seg_f = _gather_tokens(q_seg, cp, group, permuted)
+        specs = [(fwd_params.query_block_size, fwd_params.kv_block_size, False)]
+        if n_masks == 3:
+            specs.append((bwd_params.kv_block_size, bwd_params.query_block_size, False))
+            specs.append((bwd_params.query_block_size, bwd_params.kv_block_size, True))
+        masks = build_masks(q_pos_f, q_seg_f, kv_pos, kv_seg, specs, True)
+        out_h, lse_h, status = attention_forward(
+            q_h, k_h, v_h, q_pos_f, q_seg_f, kv_pos, kv_seg, masks[0],
+            (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, (0, 0))
+        ctx.save_for_backward(q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
+                              *[t for m in masks for t in m.flatten()])
+        ctx.n_masks = n_masks
+        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype)
+        ctx.status = status
+        return _heads_to_seq(out_h, cp, group, permuted)
+
+    @staticmethod
+    def backward(ctx, dout):
+        saved = ctx.saved_tensors
+        q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg = saved[:9]
+        flat = saved[9:]
+        if ctx.n_masks != 3:
+            raise ValueError("Length of mask_tensors should be equal to two")
+        masks = [AttentionMask.unflatten(flat[4 * i:4 * i + 4]) for i in range(3)]
+        scale, bwd_params, sequential, permuted, cp, group, kv_dtype = ctx.cfg
+        bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
+        if q_h.shape[1] % bq or k_h.shape[1] % bk:
+            raise AssertionError("sequence lengths must be divisible by the backward block sizes")
+        dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
+        dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
+                                                 masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
+        # every dK / dV element is complete on this rank: cast first, then exchange
+        dq = _heads_to_seq(dq_h, cp, group, permuted)
+        dk = _heads_to_seq(dk_h.to(kv_dtype), cp, group, permuted)
+        dv = _heads_to_seq(dv_h.to(kv_dtype), cp, group, permuted)
+        return (dq, dk, dv) + (None,) * 12
 
 
 def flash_attention(
@@ -299,8 +424,17 @@ def flash_attention(
     if tuple(kv_positions.shape) != (B, kv_len) or tuple(kv_segment_ids.shape) != (B, kv_len):
         raise AssertionError("kv positions / segment ids must have shape (batch, kv_seq)")
 
-    out = _FlashAttention.apply(
-        query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
-        _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
-        bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
+    can_exchange = cp > 1 and key.shape[2] % cp == 0 and kv_len == Sq * cp
+    if _cp_mode == "head_exchange" and cp > 1 and not can_exchange:
+        raise AssertionError("head_exchange context parallelism needs kv_heads % CP == 0 and self-attention lengths")
+    if can_exchange and _cp_mode != "all_gather":
+        out = _FlashAttentionHeadExchange.apply(
+            query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
+            _i32(kv_segment_ids), len(mask), float(scale), fwd_params, bwd_params,
+            bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, group)
+    else:
+        out = _FlashAttention.apply(
+            query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
+            _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
+            bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)

@@ -2,7 +2,8 @@
 
 Checks the host-side context-parallel plumbing of flash_attention without a GPU: the
 K/V all-gather into natural order and the dK/dV reduce-scatter back to the owners, with
-the chunk permutation done by the NumPy oracle instead of the CUDA kernel."""
+the chunk permutation done by the NumPy oracle instead of the CUDA kernel; and the
+all-to-all pair of the head-exchange schedule (sequence sharding <-> head sharding)."""
 import os
 import sys
 
@@ -13,7 +14,8 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from kvax_b200.ops.flash_attention import _gather_kv, _scatter_dkv, context_offsets  # noqa: E402
+from kvax_b200.ops.flash_attention import (_gather_kv, _gather_tokens, _heads_to_seq, _scatter_dkv, _seq_to_heads,  # noqa: E402
+                                            context_offsets)
 from kvax_b200.utils.sharding import Mesh  # noqa: E402
 from oracle import permutation_oracle as po  # noqa: E402
 
@@ -48,6 +50,19 @@ def main():
             local = torch.arange(loc).float()
             glob_idx = torch.where(local * 2 >= loc, local + second, local + first)
             assert torch.equal(glob_idx, gi), "global offsets do not reproduce global token indices"
+            # head exchange: this rank must receive the whole natural-order sequence for its heads
+            Hx = 2 * world
+            fullh = torch.randn(B, S, Hx, D, generator=torch.Generator().manual_seed(11))
+            globh = oracle_permute(fullh, world, False) if permuted else fullh
+            mineh = globh[:, rank * loc:(rank + 1) * loc].contiguous()
+            heads = _seq_to_heads(mineh, world, None, permuted, permute_fn=oracle_permute)
+            assert torch.equal(heads, fullh[:, :, 2 * rank:2 * rank + 2]), f"seq->heads mismatch B={B} permuted={permuted}"
+            back = _heads_to_seq(heads, world, None, permuted, permute_fn=oracle_permute)
+            assert torch.equal(back, mineh), f"heads->seq mismatch B={B} permuted={permuted}"
+            tok = torch.arange(B * S, dtype=torch.int32).view(B, S)
+            tokg = (oracle_permute(tok.view(B, S, 1, 1), world, False).view(B, S) if permuted else tok)
+            gathered = _gather_tokens(tokg[:, rank * loc:(rank + 1) * loc].contiguous(), world, None, permuted, permute_fn=oracle_permute)
+            assert torch.equal(gathered, tok), "token gather mismatch"
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

@@ -1,7 +1,8 @@
 """Worker of tests/test_gpu_context_parallel.py: one process per GPU under torchrun.
 
-Context-parallel flash attention (permute -> masks -> attention -> gradients, K/V
-all-gather and dK/dV reduce-scatter over NCCL) against the same kernels run on the whole
+Context-parallel flash attention (permute -> masks -> attention -> gradients; both
+schedules: K/V all-gather with dK/dV reduce-scatter, and the head exchange by all-to-all,
+over NCCL) against the same kernels run on the whole
 sequence on one GPU — the reference's own multi-GPU test compares CP with a non-CP run of
 the same kernels (tests/test_attention.py:520-828).  Masks per rank are also checked
 against the CPU oracle (bit-exact)."""
@@ -22,7 +23,8 @@ from oracle import mask_oracle as mo  # noqa: E402
 from oracle import permutation_oracle as po  # noqa: E402
 
 
-def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=True):
+def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=True, mode="all_gather"):
+    kv.set_context_parallel_mode(mode)
     cfg = gen.small_config(seq=seq, batch=batch, hq=hq, hkv=hkv, head_dim=128, doc_min=200, doc_max=seq // 2, pad=pad)
     inp = gen.make_inputs(cfg, seed=17, restart_positions=not sequential)
     inp["dout"] = np.where((inp["segment_ids"] != -1)[:, :, None, None], inp["dout"], 0.0).astype(np.float32)
@@ -71,9 +73,10 @@ def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=Tr
             err = (g - r).abs().max().item()
             rel = ((g - r).norm() / r.norm().clamp_min(1e-30)).item()
             worst[name] = (err, rel)
-            # out and dq come from identical kernels on identical data: exact.  dk/dv are
-            # summed over ranks in fp32 in a different order before the bf16 cast.
-            if name in ("out", "dq"):
+            # out and dq come from identical kernels on identical data: exact.  With the
+            # all-gather schedule dk/dv are summed over ranks in fp32 in a different order before
+            # the bf16 cast; with the head exchange they too are the single-GPU values.
+            if name in ("out", "dq") or mode == "head_exchange":
                 assert err == 0.0, f"{name}: CP differs from single GPU (max {err})"
             else:
                 assert rel < 4e-3 and err <= 2e-2 + r.abs().max().item() / 128, f"{name}: {err} {rel}"
@@ -90,6 +93,11 @@ def main():
     res["docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=4, hkv=2, pad=0.05, sequential=False)
     res["batch2_seqpos"] = run_case(rank, world, dev, seq=512 * world, batch=2, hq=2, hkv=2, pad=0.0, sequential=True)
     res["no_permute"] = run_case(rank, world, dev, seq=512 * world, batch=1, hq=2, hkv=1, pad=0.1, sequential=False, permuted=False)
+    hx = "head_exchange"
+    res["hx_docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=world, pad=0.05, sequential=False, mode=hx)
+    res["hx_batch2_seqpos"] = run_case(rank, world, dev, seq=512 * world, batch=2, hq=2 * world, hkv=2 * world, pad=0.0, sequential=True, mode=hx)
+    res["hx_no_permute"] = run_case(rank, world, dev, seq=512 * world, batch=1, hq=world, hkv=world, pad=0.1, sequential=False, permuted=False, mode=hx)
+    kv.set_context_parallel_mode("auto")
     dist.barrier()
     if rank == 0:
         print("cp gpu worker ok", {k: {n: (round(e, 5), round(r, 5)) for n, (e, r) in v.items()} for k, v in res.items()})
