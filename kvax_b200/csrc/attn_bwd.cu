@@ -631,27 +631,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       ok = mbar_wait(&bars[Q_SFULL0 + sbuf], (i >> 1) & 1, abort_flag, a.status, Q_SFULL0 + sbuf);
       if (!ok) break;
       tc_fence_after();
-      uint32_t v[2][32];
+      uint32_t v[2][32], dp[2][32];
       tmem_ld32(my_t1, v[0]);
       tmem_ld32(my_t1 + 32, v[1]);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        tmem_ld_wait(v[ch]);
+      tmem_ld_wait(v[0]);
+      tmem_ld_wait(v[1]);
+      auto exp_chunk = [&](int ch) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj]), c, neg_lse));
           if (partial) pv = ((keep[ch] >> jj) & 1u) ? pv : 0.f;
           v[ch][jj] = __float_as_uint(pv);
         }
-      }
-
-      // ---- dS = P * (dP - delta), written over the consumed scores of this item
+      };
+      exp_chunk(0);
+      // dP of this item was issued a whole item ago: its TMEM round trip overlaps the second
+      // half of the exponentials
       ok = mbar_wait(&bars[Q_DPFULL], i & 1, abort_flag, a.status, Q_DPFULL);
       if (!ok) break;
       tc_fence_after();
-      uint32_t dp[2][32];
       tmem_ld32(my_t2, dp[0]);
       tmem_ld32(my_t2 + 32, dp[1]);
+      exp_chunk(1);
+
+      // ---- dS = P * (dP - delta), written over the consumed scores of this item
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         tmem_ld_wait(dp[ch]);
