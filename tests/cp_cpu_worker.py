@@ -63,6 +63,27 @@ def main():
             tokg = (oracle_permute(tok.view(B, S, 1, 1), world, False).view(B, S) if permuted else tok)
             gathered = _gather_tokens(tokg[:, rank * loc:(rank + 1) * loc].contiguous(), world, None, permuted, permute_fn=oracle_permute)
             assert torch.equal(gathered, tok), "token gather mismatch"
+    if world == 4:
+        # Context parallelism inside a larger mesh: (data, context, model) = (1, 2, 2) and (2, 2): the collectives
+        # must stay inside the ranks that differ only along "context" (the reference's tests combine context
+        # parallelism with data- and tensor-parallel specs, tests/test_attention.py:520-828).
+        for names, shape in ((("data", "context", "model"), (1, 2, 2)), (("data", "context"), (2, 2))):
+            m = Mesh(names, shape)
+            cp, crank = m.shape["context"], m.coordinate("context")
+            other = rank - crank * (2 if "model" in names else 1)      # identifies the context group
+            group = m.group("context")
+            assert group is not None and dist.get_world_size(group) == cp and dist.get_rank(group) == crank
+            B, S, H, D = 1, 64 * cp, 2 * cp, 4
+            full = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(100 + other))   # differs per group
+            glob = oracle_permute(full, cp, False)
+            loc = S // cp
+            mine = glob[:, crank * loc:(crank + 1) * loc].contiguous()
+            assert torch.equal(_gather_kv(mine, cp, group, True, permute_fn=oracle_permute), full)
+            heads = _seq_to_heads(mine, cp, group, True, permute_fn=oracle_permute)
+            assert torch.equal(heads, full[:, :, 2 * crank:2 * crank + 2])
+            assert torch.equal(_heads_to_seq(heads, cp, group, True, permute_fn=oracle_permute), mine)
+            out = _scatter_dkv((crank + 1.0) * full, cp, group, True, torch.float32, permute_fn=oracle_permute)
+            assert torch.allclose(out, 3.0 * mine)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

@@ -66,6 +66,17 @@ def test_backward_mask_block_sizes(bwd_blocks):
     _check(inp, dq, dk, dv)
 
 
+@pytest.mark.parametrize("seq,head_dim", [(300, 128), (257, 64), (400, 128)])
+def test_backward_ragged_lengths(seq, head_dim):
+    """Lengths that are not multiples of the tile: the last tile of every list is cut by the
+    end of the sequence, and at 257 the LSE2 / delta rows are not 16-byte aligned, so the dK/dV
+    kernel's producer takes its lane-copy path instead of bulk copies."""
+    cfg = gen.small_config(seq=seq, batch=2, hq=4, hkv=2, head_dim=head_dim, doc_min=60, doc_max=seq, pad=0.04)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=23))
+    out, dq, dk, dv = _run_fwd_bwd(inp, fwd_blocks=(64, 64), bwd_blocks=(64, 64))
+    _check(inp, dq, dk, dv)
+
+
 def test_backward_tiny_config_c1():
     inp = _zero_pad_dout(gen.make_inputs(gen.CONFIGS["c1_tiny"], seed=0))
     _, dq, dk, dv = _run_fwd_bwd(inp, fwd_blocks=(64, 64), bwd_blocks=(64, 64))
