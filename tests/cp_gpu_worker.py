@@ -83,6 +83,60 @@ def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=Tr
     return worst
 
 
+def run_tp_case(rank, world, dev):
+    """Tensor parallelism over heads (`("data", None, "model", None)` specs, README.md:273-278 of the
+    reference), alone on 2 ranks or combined with context parallelism on a (context, model) mesh of
+    4 ranks: every rank runs its head slice and must reproduce that slice of the single-GPU result."""
+    tp = 2
+    cp = world // tp
+    seq, hq, hkv = 1024 * cp, 4 * tp, 2 * tp
+    cfg = gen.small_config(seq=seq, batch=1, hq=hq, hkv=hkv, head_dim=128, doc_min=100, doc_max=seq // 2, pad=0.05)
+    inp = gen.make_inputs(cfg, seed=29)
+    inp["dout"] = np.where((inp["segment_ids"] != -1)[:, :, None, None], inp["dout"], 0.0).astype(np.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    q, k, v, do = (t(inp[n]).to(torch.bfloat16) for n in ("q", "k", "v", "dout"))
+    pos, seg = t(inp["positions"]), t(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    m1 = kv.Mesh(("data", "context"), (1, 1), rank=0)
+    with m1, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        qf, kf, vf = (x.clone().requires_grad_(True) for x in (q, k, v))
+        masks = kv.create_attention_mask(pos, seg, pos, seg, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        of = kv.flash_attention(qf, kf, vf, pos, seg, pos, seg, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        of.backward(do)
+    mesh = kv.Mesh(("data", "context", "model"), (1, cp, tp))
+    crank, mrank = mesh.coordinate("context"), mesh.coordinate("model")
+    hs, ks = slice(mrank * hq // tp, (mrank + 1) * hq // tp), slice(mrank * hkv // tp, (mrank + 1) * hkv // tp)
+    loc = seq // cp
+    sl = slice(crank * loc, (crank + 1) * loc)
+    q_axis = "context" if cp > 1 else None
+    for mode in (("all_gather", "head_exchange") if cp > 1 else ("auto",)):
+        kv.set_context_parallel_mode(mode)
+        with mesh, kv.attention_specs(("data", q_axis, "model", None), ("data", None, "model", None)):
+            if cp > 1:
+                qp, kp, vp, dop, posp, segp = kv.permute_tokens_context_parallelism((q, k, v, do, pos, seg))
+            else:
+                qp, kp, vp, dop, posp, segp = q, k, v, do, pos, seg
+            ql = qp[:, sl, hs].contiguous().requires_grad_(True)
+            kl, vl = (x[:, sl, ks].contiguous().requires_grad_(True) for x in (kp, vp))
+            q_pos, q_seg = posp[:, sl].contiguous(), segp[:, sl].contiguous()
+            masks = kv.create_attention_mask(q_pos, q_seg, pos, seg, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+            ol = kv.flash_attention(ql, kl, vl, q_pos, q_seg, pos, seg, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+            ol.backward(dop[:, sl, hs].contiguous())
+            pick = (lambda x: kv.permute_tokens_context_parallelism(x)[:, sl]) if cp > 1 else (lambda x: x[:, sl])
+            rows = (q_seg != -1)[:, :, None, None]
+            for name, got, ref in (("out", ol, pick(of.detach())[:, :, hs]), ("dq", ql.grad, pick(qf.grad)[:, :, hs]),
+                                   ("dk", kl.grad, pick(kf.grad)[:, :, ks]), ("dv", vl.grad, pick(vf.grad)[:, :, ks])):
+                gg = torch.where(rows, got.float(), torch.zeros((), device=dev))
+                rr = torch.where(rows, ref.float(), torch.zeros((), device=dev))
+                err = (gg - rr).abs().max().item()
+                if name in ("out", "dq") or mode != "all_gather":
+                    assert err == 0.0, f"tp {mode} {name}: differs from single GPU (max {err})"
+                else:
+                    assert err <= 2e-2 + rr.abs().max().item() / 128, f"tp {mode} {name}: {err}"
+    kv.set_context_parallel_mode("auto")
+    return True
+
+
 def main():
     local_rank = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local_rank)
@@ -98,9 +152,10 @@ def main():
     res["hx_batch2_seqpos"] = run_case(rank, world, dev, seq=512 * world, batch=2, hq=2 * world, hkv=2 * world, pad=0.0, sequential=True, mode=hx)
     res["hx_no_permute"] = run_case(rank, world, dev, seq=512 * world, batch=1, hq=world, hkv=world, pad=0.1, sequential=False, permuted=False, mode=hx)
     kv.set_context_parallel_mode("auto")
+    res["tensor_parallel"] = run_tp_case(rank, world, dev)
     dist.barrier()
     if rank == 0:
-        print("cp gpu worker ok", {k: {n: (round(e, 5), round(r, 5)) for n, (e, r) in v.items()} for k, v in res.items()})
+        print("cp gpu worker ok", {k: ({n: (round(e, 5), round(r, 5)) for n, (e, r) in v.items()} if isinstance(v, dict) else v) for k, v in res.items()})
     dist.destroy_process_group()
 
 

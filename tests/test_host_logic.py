@@ -77,3 +77,26 @@ def test_flop_formula():
     assert f(2, 1024, 1024, 8, 128, 128, causal=False, forward_pass=False, backward_pass=True) == pytest.approx(base * 2.5)
     with pytest.raises(ValueError):
         f(1, 1, 1, 1, 1, 1, causal=False, forward_pass=False, backward_pass=False)
+
+
+def test_benchmark_cli_commands_and_segment_lengths():
+    """The benchmark harness exposes the reference's four commands with its option names
+    (benchmarks.py:34-407) and the reference's segment-length generator."""
+    from click.testing import CliRunner
+
+    from kvax_b200 import benchmarks as bm
+    res = CliRunner().invoke(bm.cli, ["--help"])
+    assert res.exit_code == 0
+    for cmd in ("mha", "mha_bwd", "mha_cp", "mha_cp_bwd"):
+        assert cmd in res.output
+    res = CliRunner().invoke(bm.cli, ["mha_cp_bwd", "--help"])
+    for opt in ("--num-iters", "--batch-size", "--query-seq-len", "--kv-seq-len", "--num-heads", "--num-kv-heads",
+                "--qk-head-dim", "--value-head-dim", "--assume-sequential-positions", "--num-segments",
+                "--permute-tokens-for-load-balance", "--show-attention-mask"):
+        assert opt in res.output
+    assert bm.generate_random_segments_lengths(4096, 1) is None
+    a = bm.generate_random_segments_lengths(4096, 7)
+    assert len(a) == 7 and sum(a) == 4096 and min(a) >= 1 and a == bm.generate_random_segments_lengths(4096, 7)
+    pos, seg = bm.make_positions_and_segments(2, 64, [10, 20, 34], 5)
+    assert pos.shape == (2, 64) and int(pos[1, 63]) == 63
+    assert seg[0, :10].eq(0).all() and seg[0, 10:30].eq(1).all() and seg[0, 30:59].eq(2).all() and seg[0, 59:].eq(-1).all()
