@@ -27,7 +27,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from oracle import generators as gen  # synthetic inputs (pure NumPy)
+from kvax_b200.utils import synthetic as gen  # seeded synthetic inputs (pure NumPy)
 
 METRIC = "attn TFLOP/s (unmasked FLOPs) fwd+bwd, doc-mask GQA"
 UNIT = "TFLOP/s"
@@ -197,6 +197,8 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--no-single-gpu-reference", action="store_true",
+                    help="with --gpus N > 1: skip the one-GPU run of the same workload on rank 0")
     ap.add_argument("--cp-mode", default="auto", choices=("auto", "all_gather", "head_exchange"),
                     help="context-parallel schedule for --gpus N > 1")
     ap.add_argument("--steps", type=int, default=10)
@@ -243,6 +245,32 @@ def main():
 
     kv.set_context_parallel_mode(args.cp_mode)
     hx = cp > 1 and Hkv % cp == 0 and args.cp_mode != "all_gather"
+
+    # ---- the same workload on ONE GPU (rank 0, before the context-parallel run): the N = 1 line of a scaling
+    # series uses the metric's own 32k configuration, so the strong-scaling reference for this workload is
+    # measured here and reported beside the aggregate.
+    same_1gpu = None
+    if cp > 1 and not args.no_single_gpu_reference:
+        if rank == 0:
+            g1 = torch.Generator(device=dev).manual_seed(99)
+            r1 = lambda *shape: torch.randn(*shape, generator=g1, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            q1, k1, v1, do1 = r1(B, S, Hq, D), r1(B, S, Hkv, D), r1(B, S, Hkv, D), r1(B, S, Hq, D)
+            p1, s1 = torch.from_numpy(pos_h).to(dev), torch.from_numpy(seg_h).to(dev)
+            spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
+
+            def one_gpu_step():
+                m = build_masks(p1, s1, p1, s1, spec3, True)
+                o1, l1, _ = attention_forward(q1, k1, v1, p1, s1, p1, s1, m[0], (TILE, TILE), scale)
+                attention_backward(q1, k1, v1, o1, do1, l1, p1, s1, p1, s1, m[1], m[2], (TILE, TILE), scale)
+
+            for _ in range(2):
+                one_gpu_step()
+            ms1 = cuda_time(one_gpu_step, 3)
+            same_1gpu = {"workload": cfg.name, "n_gpus": 1, "ms_per_step": ms1, "value": flops_step / (ms1 * 1e-3) / 1e12,
+                         "unit": UNIT, "steps": 3}
+            del q1, k1, v1, do1, p1, s1
+            torch.cuda.empty_cache()
+        dist.barrier()
     mesh = kv.Mesh(("data", "context"), (1, cp))
     q_spec = ("data", "context" if cp > 1 else None, None, None)
     kv_spec = ("data", None, None, None)
@@ -448,6 +476,8 @@ def main():
         line["roofline"] = roofline
     if cp == 1 and mask_info:
         line["mask_builder"] = mask_info
+    if same_1gpu:
+        line["same_workload_1gpu"] = same_1gpu
     if e2e:
         line["e2e"] = e2e
     if cp == 1 and not args.no_cpu_baseline:
