@@ -506,10 +506,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_do, &bars[Q_XFULL], x * 64, h, qt * kTile, b);
       }
       bool ok = true;
-      uint32_t e_next = __ldg(list);
+      uint32_t e_next = ldg_pinned(list);
       for (int i = 0; i < n_items && ok; ++i) {
         const int u = int(e_next & ~kPartialBit);
-        if (i + 1 < n_items) e_next = __ldg(list + i + 1);
+        if (i + 1 < n_items) e_next = ldg_pinned(list + i + 1);
         const int ks = i % kDqKStages, kuse = i / kDqKStages;
         if (kuse > 0) ok = mbar_wait(&bars[Q_KEMPTY0 + ks], (kuse - 1) & 1, abort_flag, a.status, Q_KEMPTY0 + ks);
         if (!ok) break;
@@ -610,10 +610,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int32_t* kv_seg = a.tok.kv_seg + (long long)b * a.tok.kv_len;
     const int32_t* kv_pos = a.tok.kv_pos + (long long)b * a.tok.kv_len;
     bool ok = true;
-    uint32_t e_next = __ldg(list);
+    uint32_t e_next = ldg_pinned(list);
     for (int i = 0; i < n_items && ok; ++i) {
       const uint32_t e = e_next;
-      if (i + 1 < n_items) e_next = __ldg(list + i + 1);
+      if (i + 1 < n_items) e_next = ldg_pinned(list + i + 1);
       const int c0 = int(e & ~kPartialBit) * kTile;
       const bool partial = (e & kPartialBit) != 0;
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};

@@ -79,6 +79,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Read-only global load that stays where it is written.  The kernels fetch the next tile-list
+// entry one iteration ahead; with a plain __ldg the compiler is free to sink the load to its
+// first use in the next iteration (it shortens a live range), which puts an L2 round trip on
+// the critical path of every item.  A volatile asm statement keeps its place among the other
+// volatile statements (barrier waits, TMEM traffic).
+__device__ __forceinline__ uint32_t ldg_pinned(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), tile mode, no multicast.  Coordinates are innermost
 // first; the innermost coordinate times the element size must be a multiple of 16 B.

@@ -56,6 +56,7 @@ def get_context_parallel_mode() -> str:
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 192, 256)   # what the reference accepts
 _KERNEL_HEAD_DIMS = (64, 128)                         # what the sm_100a kernels cover today
+_PADDED_HEAD_DIMS = (16, 32)                          # run as head_dim 64 on zero-padded operands
 
 
 def _i32(x):
@@ -389,10 +390,11 @@ def flash_attention(
         raise ValueError(f"The case with num_mask_tensors={len(mask)} is not supported.")
     if not query.is_cuda:
         raise _lib.KvaxB200Error("flash_attention needs CUDA tensors (there is no CPU fallback)")
-    if query.shape[-1] not in _KERNEL_HEAD_DIMS or value.shape[-1] != query.shape[-1]:
+    head_dim = query.shape[-1]
+    if head_dim not in _KERNEL_HEAD_DIMS + _PADDED_HEAD_DIMS or value.shape[-1] != head_dim:
         raise _lib.KvaxB200Error(
-            f"the sm_100a kernels cover head_dim in {_KERNEL_HEAD_DIMS} with Dqk == Dv; "
-            f"got Dqk={query.shape[-1]}, Dv={value.shape[-1]}")
+            f"the sm_100a kernels cover head_dim in {_KERNEL_HEAD_DIMS + _PADDED_HEAD_DIMS} with Dqk == Dv; "
+            f"got Dqk={head_dim}, Dv={value.shape[-1]}")
     if query.dtype not in (torch.bfloat16, torch.float16, torch.float32):
         raise _lib.KvaxB200Error(f"unsupported dtype {query.dtype}")
     in_dtype = query.dtype
@@ -401,6 +403,11 @@ def flash_attention(
         # rounded to bf16 first (the reference feeds fp32 to tl.dot, i.e. tf32 tensor cores);
         # output and gradients come back in the input dtype.
         query, key, value = query.to(torch.bfloat16), key.to(torch.bfloat16), value.to(torch.bfloat16)
+    if head_dim in _PADDED_HEAD_DIMS:
+        # Zero columns change neither Q K^T nor the first head_dim columns of P V; the output is sliced
+        # back below and autograd slices the gradients the same way.
+        pad = (0, _KERNEL_HEAD_DIMS[0] - head_dim)
+        query, key, value = (torch.nn.functional.pad(t, pad) for t in (query, key, value))
     B, Sq, Hq, _ = query.shape
     if key.shape[0] != B or value.shape[:3] != key.shape[:3] or Hq % key.shape[2]:
         raise AssertionError("inconsistent query / key / value shapes")
@@ -437,4 +444,6 @@ def flash_attention(
             query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
             _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
             bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
+    if head_dim in _PADDED_HEAD_DIMS:
+        out = out[..., :head_dim]
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)

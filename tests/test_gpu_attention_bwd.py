@@ -158,3 +158,27 @@ def test_fp32_inputs_tiny_config():
     compare("dq", q.grad.cpu().numpy(), rq, rows, max_abs=5e-2, rel_l2=1.5e-2)
     compare("dk", k.grad.cpu().numpy(), rk, rows, max_abs=5e-2, rel_l2=1.5e-2)
     compare("dv", v.grad.cpu().numpy(), rv, rows, max_abs=5e-2, rel_l2=1.5e-2)
+
+
+@pytest.mark.parametrize("head_dim", [16, 32])
+def test_small_head_dims_public_api(head_dim):
+    """head_dim 16 and 32 (accepted by the reference, flash_attention_triton.py:1397-1403) run
+    on zero-padded operands through the head_dim-64 kernels."""
+    import kvax_b200 as kv
+    cfg = gen.small_config(seq=512, batch=1, hq=4, hkv=2, head_dim=head_dim)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=31))
+    q, k, v, do = (to_bf16_cuda(inp[n]) for n in ("q", "k", "v", "dout"))
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    mesh = kv.Mesh(("data", "context"), (1, 1), rank=0)
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+        masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        assert out.shape == q.shape
+        out.backward(do)
+    rq, rk, rv = _oracle_grads(inp)
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    compare("dq", q.grad.float().cpu().numpy(), rq, rows, bf16_output=True)
+    compare("dk", k.grad.float().cpu().numpy(), rk, rows, bf16_output=True)
+    compare("dv", v.grad.float().cpu().numpy(), rv, rows, bf16_output=True)
