@@ -48,6 +48,15 @@ constexpr int kHalf = kTile / 2;                    // columns handled by one co
 // not 16-byte aligned, are copied by the producer's lanes instead.
 // Shared memory: K, V 2 x 32 KB + 2 stages x (Q, dO 64 KB + column info 2 KB).
 // ---------------------------------------------------------------------------------------
+// Sixteen register-math warps here (four per SM sub-partition: thread t owns kv row t % 128 and the 32-column quarter
+// t / 128 of every tile): the math of a tile splits by columns without any exchange between threads, and four warps
+// per scheduler hide the TMEM round trips and the shared-memory reads of LSE2 / delta that two warps left exposed.
+constexpr int kKvComputeWarps = 16;
+constexpr int kKvComputeThreads = kKvComputeWarps * 32;
+constexpr int kKvProducerWarp = kKvComputeWarps, kKvMmaWarp = kKvComputeWarps + 1;
+constexpr int kKvThreads = (kKvComputeWarps + 2) * 32;
+constexpr int kQuarter = kTile / 4;                 // columns handled by one compute thread
+
 enum KvBar { K_XFULL = 0, K_YFULL0, K_YFULL1, K_YEMPTY0, K_YEMPTY1, K_SFULL0, K_SFULL1, K_DPFULL, K_PFULL0, K_PFULL1, K_DSFULL, K_ACCFULL, K_COUNT };
 
 template <int D>
@@ -66,7 +75,7 @@ struct KvSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kKvThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                      const BwdArgs a) {
@@ -90,15 +99,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   const int q_len = a.tok.q_len;
 
   const int row = tid & (kTile - 1);           // kv row / TMEM lane of a compute thread
-  const int half = (tid >> 7) & 1;             // column half of a compute thread
+  const int quarter = tid >> 7;                 // column quarter of a compute thread
+  const int half = quarter & 1;                // epilogue: quarters 0 and 1 store D/2 columns each
   const int r = kt * kTile + row;
-  const bool is_compute = tid < kComputeThreads;
+  const bool is_compute = tid < kKvComputeThreads;
   const bool row_valid = is_compute && (r < a.tok.kv_len);
   float* dk_row = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
   float* dv_row = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
 
   if (n_items == 0) {                          // no contributing tile: zero gradients
-    if (row_valid) {
+    if (row_valid && quarter < 2) {
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) { reinterpret_cast<float4*>(dk_row)[i] = z; reinterpret_cast<float4*>(dv_row)[i] = z; }
@@ -108,11 +118,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
 
   if (tid == 0) {
     for (int i = 0; i < K_COUNT; ++i)
-      mbar_init(&bars[i], (i == K_PFULL0 || i == K_PFULL1 || i == K_DSFULL) ? kComputeThreads : 1);
+      mbar_init(&bars[i], (i == K_PFULL0 || i == K_PFULL1 || i == K_DSFULL) ? kKvComputeThreads : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == kProducerWarp) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == kKvProducerWarp) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -120,7 +130,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
   const uint32_t tT1 = tmem_base, tT2 = tmem_base + kTile;
   const uint32_t tAcc1 = tmem_base + 2 * kTile, tAcc2 = tmem_base + 3 * kTile;
 
-  if (warp == kProducerWarp) {
+  if (warp == kKvProducerWarp) {
     // ------------------------------------------------------------------ producer (whole warp; one elected lane issues)
     const int n = __shfl_sync(0xffffffffu, n_items, 0);
     const int cnt = __shfl_sync(0xffffffffu, count, 0);
@@ -206,7 +216,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       }
       __syncwarp();
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kKvMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
     constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
     constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
@@ -228,11 +238,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
         umma_ss_lo(t_addr, x_lo + off, y_lo + off, idesc_t, kk > 0);
       }
     };
-    // A operand (bf16 pairs in TMEM): K-steps 0-3 at column offset 0, K-steps 4-7 at offset 64
+    // A operand (bf16 pairs in TMEM): quarter q wrote its two K-steps at column offset 32 q
     auto issue_acc = [&](uint32_t acc_addr, uint32_t a_addr, uint32_t y_lo, uint32_t acc_on) {
 #pragma unroll
       for (int kk = 0; kk < kTile / 16; ++kk)
-        umma_ts_lo(acc_addr, a_addr + (kk >> 2) * kHalf + (kk & 3) * 8, y_lo + ((kk * 16 * 128) >> 4), idesc_acc, acc_on | (kk > 0));
+        umma_ts_lo(acc_addr, a_addr + (kk >> 1) * kQuarter + (kk & 1) * 8, y_lo + ((kk * 16 * 128) >> 4), idesc_acc, acc_on | (kk > 0));
     };
     wait(K_XFULL, 0, false);
     if (ok) wait(K_YFULL0, 0, false);
@@ -278,11 +288,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       }
       __syncwarp();
     }
-  } else {
+  } else if (is_compute) {
     // ------------------------------------------------------------------ register math
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const int cb = half * kHalf;                              // first column (within the tile) of this thread
-    const uint32_t my_t1 = tT1 + lane_base + cb;              // fp32 columns of this thread; P goes to the first 32 of them
+    const int cb = quarter * kQuarter;                        // first column (within the tile) of this thread
+    const uint32_t my_t1 = tT1 + lane_base + cb;              // fp32 columns of this thread; P goes to the first 16 of them
     const uint32_t my_t2 = tT2 + lane_base + cb;
     const float c = a.scale_log2e;
     const RowBounds rb = load_bounds(a.mask, b, min(r, a.tok.kv_len - 1));
@@ -309,39 +319,33 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       ok = mbar_wait(&bars[K_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, K_YFULL0 + st);
       if (!ok) break;
 
-      // element mask of partial tiles, one bit per column of this thread's half
-      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
-      if (partial) {
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch)
-          keep[ch] = keep_bits32<true>(rb, c0 + cb + ch * 32, q_len, row_valid, kv_seg, kv_pos, cs + cb + ch * 32, cs + kTile + cb + ch * 32);
-      }
+      // element mask of partial tiles, one bit per column of this thread's quarter
+      uint32_t keep = 0xffffffffu;
+      if (partial) keep = keep_bits32<true>(rb, c0 + cb, q_len, row_valid, kv_seg, kv_pos, cs + cb, cs + kTile + cb);
 
-      // ---- P = exp2(S * scale*log2e - LSE2): the 64 values of this thread stay in registers
+      // ---- P = exp2(S * scale*log2e - LSE2): the 32 values of this thread stay in registers
       ok = mbar_wait(&bars[K_SFULL0 + st], (i >> 1) & 1, abort_flag, a.status, K_SFULL0 + st);
       if (!ok) break;
       tc_fence_after();
-      uint32_t v[2][32];
-      tmem_ld32(my_t1, v[0]);
-      tmem_ld32(my_t1 + 32, v[1]);
+      uint32_t v[32];
+      tmem_ld32(my_t1, v);
+      tmem_ld_wait(v);
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        tmem_ld_wait(v[ch]);
+      for (int jj = 0; jj < 32; jj += 4) {
+        const float4 ls = cs_lse[jj >> 2];
+        const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 4) {
-          const float4 ls = cs_lse[(ch * 32 + jj) >> 2];
-          const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj + t]), c, -l4[t]));
-            if (partial) pv = ((keep[ch] >> (jj + t)) & 1u) ? pv : 0.f;
-            v[ch][jj + t] = __float_as_uint(pv);
-          }
+        for (int t = 0; t < 4; ++t) {
+          float pv = fast_exp2(fmaf(__uint_as_float(v[jj + t]), c, -l4[t]));
+          if (partial) pv = ((keep >> (jj + t)) & 1u) ? pv : 0.f;
+          v[jj + t] = __float_as_uint(pv);
         }
+      }
+      {
         uint32_t pk[16];
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
-        tmem_st16(my_t1 + ch * 16, pk);
+        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1]));
+        tmem_st16(my_t1, pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -351,26 +355,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       ok = mbar_wait(&bars[K_DPFULL], i & 1, abort_flag, a.status, K_DPFULL);
       if (!ok) break;
       tc_fence_after();
-      uint32_t dp[2][32];
-      tmem_ld32(my_t2, dp[0]);
-      tmem_ld32(my_t2 + 32, dp[1]);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        tmem_ld_wait(dp[ch]);
+      uint32_t dp[32];
+      tmem_ld32(my_t2, dp);
+      tmem_ld_wait(dp);
+      {
         uint32_t ds[16];
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 4) {
-          const float4 dl = cs_dl[(ch * 32 + jj) >> 2];
-          const float d0 = __uint_as_float(v[ch][jj + 0]) * (__uint_as_float(dp[ch][jj + 0]) - dl.x);
-          const float d1 = __uint_as_float(v[ch][jj + 1]) * (__uint_as_float(dp[ch][jj + 1]) - dl.y);
-          const float d2 = __uint_as_float(v[ch][jj + 2]) * (__uint_as_float(dp[ch][jj + 2]) - dl.z);
-          const float d3 = __uint_as_float(v[ch][jj + 3]) * (__uint_as_float(dp[ch][jj + 3]) - dl.w);
+          const float4 dl = cs_dl[jj >> 2];
+          const float d0 = __uint_as_float(v[jj + 0]) * (__uint_as_float(dp[jj + 0]) - dl.x);
+          const float d1 = __uint_as_float(v[jj + 1]) * (__uint_as_float(dp[jj + 1]) - dl.y);
+          const float d2 = __uint_as_float(v[jj + 2]) * (__uint_as_float(dp[jj + 2]) - dl.z);
+          const float d3 = __uint_as_float(v[jj + 3]) * (__uint_as_float(dp[jj + 3]) - dl.w);
           ds[jj >> 1] = pack_bf16(d0, d1);
           ds[(jj >> 1) + 1] = pack_bf16(d2, d3);
         }
-        // both 32-column chunks were loaded before the first store, so writing over the
-        // first 32 columns is safe
-        tmem_st16(my_t2 + ch * 16, ds);
+        tmem_st16(my_t2, ds);      // over the first 16 of this thread's 32 dP columns, all of which are in registers
       }
       tmem_st_wait();
       tc_fence_before();
@@ -378,9 +378,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     }
 
     if (ok) ok = mbar_wait(&bars[K_ACCFULL], 0, abort_flag, a.status, K_ACCFULL);
-    if (ok) {
+    if (ok && quarter < 2) {
       tc_fence_after();
-      // each thread stores D/2 columns of its row: columns [half*D/2, (half+1)*D/2)
+      // threads of quarters 0 and 1 store D/2 columns of their row: columns [half*D/2, (half+1)*D/2)
 #pragma unroll
       for (int ch = 0; ch < D / 64; ++ch) {
         uint32_t v1[32], v2[32];
@@ -404,7 +404,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kProducerWarp) {
+  if (warp == kKvProducerWarp) {
     if (*abort_flag && lane == 0) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) { }
@@ -749,7 +749,7 @@ int launch_dkdv(const BwdLaunch& L, cudaStream_t stream) {
   auto kern = attn_bwd_dkdv_kernel<D>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
   dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
-  kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // K, V, Q, dO
+  kern<<<grid, kKvThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // K, V, Q, dO
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
 
