@@ -357,7 +357,7 @@ def main():
                         "peak_source": peaks["source"] + " burst",
                         # dram__bytes_read.sum + dram__bytes_write.sum of one dK/dV launch on this workload, from
                         # the ncu capture summarised in profiles/ncu_attn_bwd_c4_docmask_32k.txt (null elsewhere)
-                        "traffic": 7.52e9 if name == "c4_docmask_32k" else None, "traffic_unit": "bytes per launch",
+                        "traffic": 7.84e9 if name == "c4_docmask_32k" else None, "traffic_unit": "bytes per launch",
                         "fwd_kernel_tflops": flops_fwd / (parts["fwd_kernel_ms"] * 1e-3) / 1e12,
                         "dq_kernel_tflops": 0.5 * flops_fwd / (parts["dq_kernel_ms"] * 1e-3) / 1e12,
                         "step_frac_of_burst": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
