@@ -99,7 +99,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         with open(self.path) as f:
             for line in f:
@@ -107,7 +107,7 @@ class ClockSampler:
                 if len(parts) < 9:
                     continue
                 try:
-                    sm.append(float(parts[1])); mx.append(float(parts[2]))
+                    sm.append(float(parts[1])); mx.append(float(parts[2])); pw.append(float(parts[3]))
                 except ValueError:
                     continue
                 for nm, val in zip(names, parts[5:9]):
@@ -115,7 +115,8 @@ class ClockSampler:
                         reasons.add(nm)
         os.unlink(self.path)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+                    reasons=sorted(reasons), samples=len(sm), power_w_median=statistics.median(pw) if pw else None,
+                    power_w_max=max(pw) if pw else None)
 
 
 def cuda_time(fn, iters):
