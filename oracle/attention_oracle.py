@@ -10,9 +10,15 @@ Restates the dense masked attention the reference's tests compare their kernels 
                                            shared by Hq/Hkv query heads
 The dense op itself is jax.nn.dot_product_attention (third-party, jax>=0.4.34 per the
 reference's pyproject.toml, not vendored and not installed here) so its published
-definition is restated.  The reference holds no golden vectors for attention outputs
-(its tests compare two GPU implementations): PARITY UNPINNED for this module, other
-than through the analytic gradient check in tests/test_oracle_attention.py.
+definition is restated.
+
+Parity is pinned: tests/golden/attn_*.npz hold the outputs of the reference's own
+`flash_attention_triton_forward` and `flash_attention_backward` (host code and Triton
+kernels, run by Triton's CPU interpreter through tests/golden/make_attention_golden.py) on
+six small seeded cases (GQA and MHA, head_dim 64 / 128, restarting and global positions,
+`assume_sequential_positions`, mixed block sizes, ragged lengths, decode);
+tests/test_oracle_attention.py checks this restatement against them to 2e-5 for O, LSE2,
+dQ, dK and dV on every row the reference specifies.
 
 Layouts follow the public API: q (B, Sq, Hq, D), k/v (B, Skv, Hkv, D).
 """

@@ -46,3 +46,9 @@ def oracle_fwd(inp, q=None, k=None, v=None):
     p, s = inp["positions"], inp["segment_ids"]
     return ao.attention_forward(bf16_round(inp["q"]), bf16_round(inp["k"]), bf16_round(inp["v"]),
                                 p, s, p, s, inp["scale"], dtype=np.float32)
+
+
+def bf16_bits_to_f32(bits):
+    """int16 array holding bf16 bit patterns -> float32 values (how the attention fixtures store
+    their bf16-representable inputs)."""
+    return (np.asarray(bits).astype(np.uint16).astype(np.uint32) << 16).view(np.float32)
