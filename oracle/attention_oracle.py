@@ -15,8 +15,9 @@ definition is restated.
 Parity is pinned: tests/golden/attn_*.npz hold the outputs of the reference's own
 `flash_attention_triton_forward` and `flash_attention_backward` (host code and Triton
 kernels, run by Triton's CPU interpreter through tests/golden/make_attention_golden.py) on
-six small seeded cases (GQA and MHA, head_dim 64 / 128, restarting and global positions,
-`assume_sequential_positions`, mixed block sizes, ragged lengths, decode);
+eight small seeded cases (GQA and MHA, head_dim 64 / 128, restarting and global positions,
+`assume_sequential_positions`, mixed block sizes, ragged lengths, decode, the two ranks of a
+context-parallel run);
 tests/test_oracle_attention.py checks this restatement against them to 2e-5 for O, LSE2,
 dQ, dK and dV on every row the reference specifies.
 

@@ -48,8 +48,28 @@ import make_mask_golden as mg  # noqa: E402  (stubs and the segment generator)
 def _install_attention_stubs(ref_root: str) -> None:
     mg._install_stubs(ref_root)
     jnp, chex, jt, jax = (sys.modules[n] for n in ("jax.numpy", "chex", "jax_triton", "jax"))
-    for nm in ("zeros", "ones", "concatenate", "sum", "arange", "asarray"):
+    for nm in ("concatenate", "sum", "arange", "asarray"):
         setattr(jnp, nm, getattr(np, nm))
+
+    class _JaxLikeArray(np.ndarray):
+        """ndarray with JAX's functional update `x.at[idx].set(v)` (used by the backward host code)."""
+
+        @property
+        def at(self):
+            arr = self
+
+            class _At:
+                def __getitem__(self, idx):
+                    class _Set:
+                        def set(self, value):
+                            out = np.array(arr, copy=True)
+                            out[idx] = value
+                            return out.view(_JaxLikeArray)
+                    return _Set()
+            return _At()
+
+    jnp.zeros = lambda *a, **k: np.zeros(*a, **k).view(_JaxLikeArray)
+    jnp.ones = lambda *a, **k: np.ones(*a, **k).view(_JaxLikeArray)
     for nm in ("assert_axis_dimension_comparator", "assert_is_divisible"):
         setattr(chex, nm, lambda *a, **k: None)
 
@@ -140,12 +160,16 @@ def _bf16_bits(x):
 
 CASES = [
     # name, B, Sq, Skv, Hq, Hkv, D, docs, pad, restart, fwd(q,kv), bwd(q,kv) or None, sequential
+    # (names starting with "cp2" run the context-parallel code path once per rank: permuted local queries
+    #  against the full keys / values, `jax.lax.axis_index` answering with the rank)
     ("tiny_c1", 1, 512, 512, 4, 2, 64, 3, 32, True, (64, 64), (64, 64), False),
     ("d128_blk128", 1, 384, 384, 2, 1, 128, 2, 40, False, (128, 128), (128, 128), False),
     ("d128_sequential", 1, 384, 384, 2, 1, 128, 2, 40, False, (128, 128), (128, 128), True),
     ("mixed_blocks_mha", 2, 256, 256, 2, 2, 64, 4, 20, True, (128, 64), (64, 128), False),
     ("ragged_fwd", 2, 200, 200, 2, 1, 64, 2, 13, False, (64, 64), None, False),
     ("decode_fwd", 2, 1, 320, 4, 2, 64, 1, 0, False, (64, 64), None, False),
+    ("cp2_rank0_sequential", 1, 256, 512, 2, 1, 64, 3, 24, False, (64, 64), (64, 64), True),
+    ("cp2_rank1_sequential", 1, 256, 512, 2, 1, 64, 3, 24, False, (64, 64), (64, 64), True),
 ]
 
 
@@ -156,22 +180,36 @@ def main(ref_root: str, out_dir: str) -> None:
     mc = importlib.import_module("kvax.ops.mask_creator")
     from kvax.utils.common import FlashAttentionParamsConfig
 
+    import types
+    jax = sys.modules["jax"]
     rng = np.random.default_rng(1)
     for (name, B, Sq, Skv, Hq, Hkv, D, docs, pad, restart, fwd, bwd, sequential) in CASES:
         S = max(Sq, Skv)
+        cp, rank = (2, int(name[8])) if name.startswith("cp2_rank") else (1, 0)
+        if cp > 1:      # both ranks see the same global sequence
+            rng = np.random.default_rng(7)
+            jax.lax = types.SimpleNamespace(axis_index=lambda axis: rank, psum=lambda x, axis: x * cp)
         pos, seg = mg._segments(rng, B, S, docs, pad, restart)
         kv_pos, kv_seg = pos[:, :Skv].copy(), seg[:, :Skv].copy()
         if name == "decode_fwd":   # one query token at per-row positions against a padded KV cache
             starts = np.array([17, 250], np.int32)
             q_pos, q_seg = starts[:, None].copy(), np.zeros((B, 1), np.int32)
             kv_seg = np.where(np.arange(Skv)[None, :] > starts[:, None], -1, 0).astype(np.int32)
+        elif cp > 1:               # the caller permutes the query side; this rank holds one slice of it
+            q_pos = mg._permute(pos, cp)[:, rank * Sq:(rank + 1) * Sq].copy()
+            q_seg = mg._permute(seg, cp)[:, rank * Sq:(rank + 1) * Sq].copy()
         else:
             q_pos, q_seg = pos[:, :Sq].copy(), seg[:, :Sq].copy()
         scale = float(D) ** -0.5
         # the reference's internal layout is (batch, heads, seq, dim)
+        if cp > 1:                 # same K / V on both ranks, rank-specific Q / dO
+            k = _bf16_values(rng, (B, Hkv, Skv, D))
+            v = _bf16_values(rng, (B, Hkv, Skv, D))
+            rng = np.random.default_rng(70 + rank)
         q = _bf16_values(rng, (B, Hq, Sq, D))
-        k = _bf16_values(rng, (B, Hkv, Skv, D))
-        v = _bf16_values(rng, (B, Hkv, Skv, D))
+        if cp == 1:
+            k = _bf16_values(rng, (B, Hkv, Skv, D))
+            v = _bf16_values(rng, (B, Hkv, Skv, D))
         do = _bf16_values(rng, (B, Hq, Sq, D))
         do = np.where((q_seg != -1)[:, None, :, None], do, 0.0).astype(np.float32)
         fp = FlashAttentionParamsConfig(query_block_size=fwd[0], kv_block_size=fwd[1], num_warps=4, num_stages=2)
@@ -186,15 +224,17 @@ def main(ref_root: str, out_dir: str) -> None:
                 q_pos, q_seg, kv_pos, kv_seg, skip_pad_tokens=True, **kw)) for kw in specs)
         out, res = fa.flash_attention_triton_forward(
             q, k, v, q_pos, q_seg, kv_pos, kv_seg, masks, scale, None, fp, bp,
-            assume_sequential_positions=sequential)
+            assume_sequential_positions=sequential,
+            context_parallelism_mesh_axis_name="context" if cp > 1 else None)
         lse = np.asarray(res[-1])[:, :, :Sq]
         to_bshd = lambda a: np.ascontiguousarray(np.asarray(a).transpose(0, 2, 1, 3))
         fix = dict(q=_bf16_bits(to_bshd(q)), k=_bf16_bits(to_bshd(k)), v=_bf16_bits(to_bshd(v)),
                    dout=_bf16_bits(to_bshd(do)), q_pos=q_pos, q_seg=q_seg, kv_pos=kv_pos, kv_seg=kv_seg,
                    scale=np.float32(scale), fwd=np.array(fwd), bwd=np.array(bwd if bwd else (0, 0)),
-                   sequential=np.array(sequential), out=to_bshd(out).astype(np.float32), lse2=lse.astype(np.float32))
+                   sequential=np.array(sequential), cp=np.array(cp), rank=np.array(rank), out=to_bshd(out).astype(np.float32), lse2=lse.astype(np.float32))
         if bwd is not None:
-            grads = fa.flash_attention_backward(scale, None, fp, bp, sequential, False, True, None, False, res, do)
+            grads = fa.flash_attention_backward(scale, None, fp, bp, sequential, False, True,
+                                                "context" if cp > 1 else None, False, res, do)
             fix.update(dq=to_bshd(grads[0]).astype(np.float32), dk=to_bshd(grads[1]).astype(np.float32),
                        dv=to_bshd(grads[2]).astype(np.float32))
         np.savez_compressed(os.path.join(out_dir, f"attn_{name}.npz"), **fix)

@@ -17,7 +17,7 @@ GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[5:-4] for p in GOLDEN])
 def test_kernels_match_reference_outputs(path):
-    from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status
+    from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status, context_offsets
     from kvax_b200.ops.mask_creator import build_masks
 
     z = np.load(path)
@@ -26,13 +26,17 @@ def test_kernels_match_reference_outputs(path):
     qp, qs, kp, ks = (i32_cuda(z[n]) for n in ("q_pos", "q_seg", "kv_pos", "kv_seg"))
     scale, seq = float(z["scale"]), bool(z["sequential"])
     fwd = tuple(int(x) for x in z["fwd"])
+    # per-rank fixtures of the context-parallel path: local (permuted) queries against the full keys / values,
+    # sequential positions given by global offsets of the two halves of the local queries
+    cp, rank = int(z["cp"]), int(z["rank"])
+    offsets = context_offsets(rank, cp, q.shape[1], True)
     has_bwd = "dq" in z.files
     specs = [(fwd[0], fwd[1], False)]
     if has_bwd:
         bq, bk = (int(x) for x in z["bwd"])
         specs += [(bk, bq, False), (bq, bk, True)]
     masks = build_masks(qp, qs, kp, ks, specs, True)
-    out, lse, st = attention_forward(q, k, v, qp, qs, kp, ks, masks[0], fwd, scale, seq)
+    out, lse, st = attention_forward(q, k, v, qp, qs, kp, ks, masks[0], fwd, scale, seq, offsets)
     torch.cuda.synchronize()
     check_status(st, "attn_fwd")
     rows = (z["q_seg"] != -1) & np.isfinite(z["lse2"]).all(axis=1)
@@ -41,7 +45,7 @@ def test_kernels_match_reference_outputs(path):
     lse_err = np.abs(np.where(rows[:, None, :], lse.cpu().numpy() - z["lse2"], 0)).max()
     assert lse_err <= 2e-2, f"lse2: {lse_err}"
     if has_bwd:
-        dq, dk, dv, st2 = attention_backward(q, k, v, out, do, lse, qp, qs, kp, ks, masks[1], masks[2], (bq, bk), scale, seq)
+        dq, dk, dv, st2 = attention_backward(q, k, v, out, do, lse, qp, qs, kp, ks, masks[1], masks[2], (bq, bk), scale, seq, offsets)
         torch.cuda.synchronize()
         check_status(st2, "attn_bwd")
         krows = (z["kv_seg"] != -1)[:, :, None, None]

@@ -19,7 +19,7 @@ GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)
 
 
 def test_fixtures_present():
-    assert len(GOLDEN) >= 6
+    assert len(GOLDEN) >= 8
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[5:-4] for p in GOLDEN])
