@@ -175,8 +175,7 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   fill_list(&a.list, sa);
   a.mask = mv; a.tok = sa.tok;
   a.out = static_cast<__nv_bfloat16*>(p->out); a.lse = p->lse; a.status = p->status;
-  a.q = static_cast<const __nv_bfloat16*>(p->q);
-  for (int i = 0; i < 3; ++i) { a.o_strides[i] = s.o_strides[i]; a.q_strides[i] = s.q_strides[i]; }
+  for (int i = 0; i < 3; ++i) a.o_strides[i] = s.o_strides[i];
   a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;

@@ -42,10 +42,10 @@ constexpr int kKStages = 3, kVStages = 3;
 
 enum FwdBar {
   B_QFULL = 0,
-  B_KFULL0, B_KFULL1, B_KFULL2, B_KEMPTY0, B_KEMPTY1, B_KEMPTY2,
+  B_KFULL0, B_KFULL1, B_KFULL2,              // a K stage is free once S_FULL of the entry that used it has completed
   B_VFULL0, B_VFULL1, B_VFULL2, B_VEMPTY0, B_VEMPTY1, B_VEMPTY2,
   B_SFULL0, B_SFULL1, B_PFULL0, B_PFULL1,
-  B_OFULL, B_LFULL, B_COUNT
+  B_LFULL, B_COUNT
 };
 
 template <int D>

@@ -26,9 +26,7 @@ struct FwdArgs {
   TileList list;            // one row per query tile
   MaskView mask;            // forward mask (query-outer)
   TokenInfo tok;
-  const __nv_bfloat16* q;   // read directly (rows go to TMEM as the A operand of Q K^T)
-  long long q_strides[3];   // batch, seq, head (elements)
-  __nv_bfloat16* out;
+  __nv_bfloat16* out;       // Q, K and V reach the kernel through their tensor maps
   float* lse;               // (B, Hq, Sq)
   int32_t* status;
   long long o_strides[3];   // batch, seq, head (elements)
