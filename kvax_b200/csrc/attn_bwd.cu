@@ -10,9 +10,10 @@
 //     P  = exp2(T1 * scale*log2e - LSE2), masked;  dS = P * (T2 - delta)   (registers)
 //     P, dS -> bf16 -> TMEM
 //     dV += P^T dO (dK/dV kernel);  dQ += dS K  or  dK += dS^T Q   tcgen05, A from TMEM
-// Warps 0-7 do the register math (thread t: outer row t % 128 = TMEM lane, column half
-// t / 128 of every tile), warp 8 is the TMA producer, warp 9 issues the MMAs: the whole warp
-// runs the issue loop and one elected lane executes the tcgen05 instructions.  The MMA
+// The first warps do the register math (thread t: outer row t % 128 = TMEM lane and a column
+// slice t / 128 of every tile: halves with 8 warps in the dQ kernel, quarters with 16 warps in
+// the dK/dV kernel), the next warp is the TMA producer and the last one issues the MMAs: the
+// whole warp runs the issue loop and one elected lane executes the tcgen05 instructions.  The MMA
 // order is software-pipelined so that the tensor pipe has work while the register math of
 // the neighbouring step runs; tcgen05.mma instructions of one thread execute in issue
 // order, which is what lets a later MMA overwrite TMEM columns an earlier one reads.
