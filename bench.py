@@ -361,6 +361,9 @@ def main():
                         "traffic": 7.84e9 if name == "c4_docmask_32k" else None, "traffic_unit": "bytes per launch",
                         "fwd_kernel_tflops": flops_fwd / (parts["fwd_kernel_ms"] * 1e-3) / 1e12,
                         "dq_kernel_tflops": 0.5 * flops_fwd / (parts["dq_kernel_ms"] * 1e-3) / 1e12,
+                        # MMA work the step executes: 2 GEMMs forward + 3 in the dQ kernel + 4 in the dK/dV kernel = 4.5
+                        # forward units, of which 3.5 count as useful (S and dP are computed twice)
+                        "executed_mma_tflops": 4.5 * flops_fwd / (ms_step * 1e-3) / 1e12,
                         "step_frac_of_burst": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                         "step_frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
                         "step_frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / 2250.0}
