@@ -100,3 +100,14 @@ def test_benchmark_cli_commands_and_segment_lengths():
     pos, seg = bm.make_positions_and_segments(2, 64, [10, 20, 34], 5)
     assert pos.shape == (2, 64) and int(pos[1, 63]) == 63
     assert seg[0, :10].eq(0).all() and seg[0, 10:30].eq(1).all() and seg[0, 30:59].eq(2).all() and seg[0, 59:].eq(-1).all()
+
+
+def test_context_parallel_mode_switch():
+    import kvax_b200 as kv
+    assert kv.get_context_parallel_mode() == "auto"
+    for mode in ("all_gather", "head_exchange", "auto"):
+        kv.set_context_parallel_mode(mode)
+        assert kv.get_context_parallel_mode() == mode
+    with pytest.raises(ValueError):
+        kv.set_context_parallel_mode("ring")
+    assert kv.get_context_parallel_mode() == "auto"
