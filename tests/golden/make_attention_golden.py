@@ -20,7 +20,7 @@ Three shims make that possible without JAX and without a GPU; none changes what 
   * inside `@triton.jit` functions the Python keywords `and` / `or` are rewritten to `&` / `|`
     on the syntax tree (compiled Triton maps them to logical ops on tensors; plain Python
     would ask a tensor for its truth value).  The rewritten module is a build product written
-    to oracle/_ref/ (ignored by git), never committed.
+    to oracle/_ref/ (ignored by git) and deleted again at the end of the run.
 
 Inputs are drawn as bf16-representable fp32 values, so that an implementation computing on
 bf16 operands sees exactly the same numbers.  dO is zero on PAD rows (the reference's tests
@@ -239,6 +239,7 @@ def main(ref_root: str, out_dir: str) -> None:
                        dv=to_bshd(grads[2]).astype(np.float32))
         np.savez_compressed(os.path.join(out_dir, f"attn_{name}.npz"), **fix)
         print("wrote", name, {k_: getattr(v_, "shape", None) for k_, v_ in fix.items() if k_ in ("out", "dq", "dk")})
+    os.remove(os.path.join(repo, "oracle", "_ref", "flash_attention_triton_interp.py"))
 
 
 if __name__ == "__main__":
