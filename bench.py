@@ -44,6 +44,23 @@ def measured_peaks():
     return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
 
 
+def profile_traffic(kernel: str, workload: str):
+    """DRAM bytes per launch of `kernel` on `workload` as recorded by the committed ncu summary
+    (profiles/*.txt: a line `traffic_bytes_per_launch <kernel> <workload> <bytes>`); (None, reason)
+    when no capture of that pair has been summarised."""
+    pdir = os.path.join(ROOT, "profiles")
+    if os.path.isdir(pdir):
+        for fn in sorted(os.listdir(pdir)):
+            if not fn.endswith((".txt", ".md")):
+                continue
+            with open(os.path.join(pdir, fn)) as f:
+                for line in f:
+                    parts = line.split()
+                    if len(parts) >= 4 and parts[0] == "traffic_bytes_per_launch" and parts[1] == kernel and parts[2] == workload:
+                        return float(parts[3]), f"profiles/{fn}"
+    return None, f"no ncu capture of {kernel} on {workload} summarised under profiles/"
+
+
 def tight_tiles(pos, seg):
     """Tile pairs with at least one unmasked element of segment AND causal AND non-PAD —
     the work the throughput is normalised by.  Pure NumPy on the host arrays."""
@@ -335,7 +352,7 @@ def main():
             qd, kd, vd = q.detach(), k.detach(), v.detach()
             out, lse, st, ws_f = attention_forward(qd, kd, vd, q_pos, q_seg, kv_pos, kv_seg, masks[0], (TILE, TILE), scale, stages=3)
             dq, dk, dv, st2, ws_b = attention_backward(qd, kd, vd, out, do, lse, q_pos, q_seg, kv_pos, kv_seg, masks[1], masks[2],
-                                                       (TILE, TILE), scale, stages=15)
+                                                       (TILE, TILE), scale, stages=63)
             torch.cuda.synchronize()
             check_status(st, "attn_fwd"); check_status(st2, "attn_bwd")
             it = max(5, K)
@@ -343,27 +360,33 @@ def main():
                                                                                 bwd_params=params, calc_bwd_mask=True), it)
             parts["fwd_kernel_ms"] = cuda_time(lambda: attention_forward(qd, kd, vd, q_pos, q_seg, kv_pos, kv_seg, masks[0], (TILE, TILE),
                                                                          scale, workspace=ws_f, stages=2, out=out, lse=lse), it)
-            bw = lambda stg: cuda_time(lambda: attention_backward(qd, kd, vd, out, do, lse, q_pos, q_seg, kv_pos, kv_seg, masks[1], masks[2],
-                                                                  (TILE, TILE), scale, workspace=ws_b, stages=stg, grads=(dq, dk, dv)), it)
-            parts["tile_lists_ms"] = bw(1)
-            parts["delta_ms"] = bw(2)
-            parts["dq_kernel_ms"] = bw(4)
-            parts["dkdv_kernel_ms"] = bw(8)
-            # The dK/dV kernel is the dominant launch.  Of the five GEMMs the backward needs
-            # per tile pair (S, dP, dV, dK, dQ = 2.5 x forward) it performs four.
-            dk_flops = 2.0 * flops_fwd
-            ach = dk_flops / (parts["dkdv_kernel_ms"] * 1e-3) / 1e12
-            roofline = {"bound": "tensor", "kernel": "attn_bwd_dkdv_kernel<128> (dK/dV)", "achieved": ach,
+            bw = lambda stg, ws, mode: cuda_time(lambda: attention_backward(
+                qd, kd, vd, out, do, lse, q_pos, q_seg, kv_pos, kv_seg, masks[1], masks[2], (TILE, TILE), scale,
+                workspace=ws, stages=stg, grads=(dq, dk, dv), mode=mode), it)
+            parts["tile_lists_ms"] = bw(1, ws_b, "fused")
+            parts["delta_and_zero_fill_ms"] = bw(2, ws_b, "fused")
+            parts["fused_bwd_kernel_ms"] = bw(16, ws_b, "fused")
+            parts["dq_cast_ms"] = bw(32, ws_b, "fused")
+            # the bit-reproducible two-kernel backward, for comparison (not part of the timed step)
+            ws_t = torch.empty_like(ws_b)
+            attention_backward(qd, kd, vd, out, do, lse, q_pos, q_seg, kv_pos, kv_seg, masks[1], masks[2], (TILE, TILE), scale,
+                               workspace=ws_t, stages=15, grads=(dq, dk, dv), mode="two_kernel")
+            parts["two_kernel_dq_ms"] = bw(4, ws_t, "two_kernel")
+            parts["two_kernel_dkdv_ms"] = bw(8, ws_t, "two_kernel")
+            del ws_t
+            # The fused backward kernel is the dominant launch: all five products the backward needs per tile pair
+            # (S, dP, dV, dK, dQ = 2.5 x forward).
+            bwd_flops = 2.5 * flops_fwd
+            ach = bwd_flops / (parts["fused_bwd_kernel_ms"] * 1e-3) / 1e12
+            traffic, traffic_note = profile_traffic("attn_bwd_fused_kernel", name)
+            roofline = {"bound": "tensor", "kernel": "attn_bwd_fused_kernel<128> (dK, dV, dQ)", "achieved": ach,
                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"],
                         "peak_source": peaks["source"] + " burst",
-                        # dram__bytes_read.sum + dram__bytes_write.sum of one dK/dV launch on this workload, from
-                        # the ncu capture summarised in profiles/ncu_attn_bwd_c4_docmask_32k.txt (null elsewhere)
-                        "traffic": 7.84e9 if name == "c4_docmask_32k" else None, "traffic_unit": "bytes per launch",
+                        "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_note,
                         "fwd_kernel_tflops": flops_fwd / (parts["fwd_kernel_ms"] * 1e-3) / 1e12,
-                        "dq_kernel_tflops": 0.5 * flops_fwd / (parts["dq_kernel_ms"] * 1e-3) / 1e12,
-                        # MMA work the step executes: 2 GEMMs forward + 3 in the dQ kernel + 4 in the dK/dV kernel = 4.5
-                        # forward units, of which 3.5 count as useful (S and dP are computed twice)
-                        "executed_mma_tflops": 4.5 * flops_fwd / (ms_step * 1e-3) / 1e12,
+                        "fwd_kernel_frac": flops_fwd / (parts["fwd_kernel_ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                        # MMA work the step executes = the work that counts: 2 products forward + 5 backward
+                        "executed_mma_tflops": 3.5 * flops_fwd / (ms_step * 1e-3) / 1e12,
                         "step_frac_of_burst": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                         "step_frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
                         "step_frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / 2250.0}
@@ -463,8 +486,9 @@ def main():
         return
 
     value = flops_step / (ms_step * 1e-3) / 1e12
-    # mask(2) fwd(sched+attn) bwd(2 sched, delta, dq, dkdv) [+ token permutes; the head exchange rebuilds the masks]
-    kernels_per_step = 2 + (2 + 1) + (2 + 1 + 2) + (0 if cp == 1 else (12 if hx else 6))
+    # mask (2), forward (summaries, lists, order, attention), backward (summaries, lists, order, delta, fused kernel, dQ cast)
+    # [+ token permutes; the head exchange rebuilds the masks]
+    kernels_per_step = 2 + (3 + 1) + (3 + 1 + 1 + 1) + (0 if cp == 1 else (12 if hx else 6))
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": cp, "steps": K, "warmup": W,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

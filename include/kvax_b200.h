@@ -44,6 +44,13 @@ enum { KVAX_B200_BF16 = 0 };
 const char* kvax_b200_version(void);
 const char* kvax_b200_error_string(int code);
 
+/* The `status` word of the attention entry points may live in page-locked host memory, so
+ * that the host can look at it at any time without synchronising the stream.  This returns
+ * the address under which the current device reaches such a word (KVAX_B200_EUNSUPPORTED
+ * when the memory is not page-locked and mapped).  Allocates nothing.  (No counterpart in
+ * the reference, whose custom calls have no status channel.) */
+int kvax_b200_host_word_device_pointer(void* host_ptr, void** device_ptr);
+
 /* ------------------------------------------------------------------------------------
  * Block-mask builder.
  * Replaces compute_attention_mask_kernel (kvax/ops/mask_creator.py:26-152) together with
@@ -77,6 +84,7 @@ typedef struct kvax_b200_mask_params {
 } kvax_b200_mask_params;
 
 size_t kvax_b200_mask_workspace_bytes(const kvax_b200_mask_params* p);
+/* `workspace`: device memory, 256-byte aligned, at least kvax_b200_mask_workspace_bytes(p). */
 int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
                          kvax_b200_stream_t stream);
 
@@ -99,7 +107,9 @@ int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t
  * launches nothing.  Every GPU that loads the library holds the 4 MiB until exit.
  *
  * The first call on each device looks up the device address of the area (with that
- * device current); make that first call outside any stream capture.  All calls on a
+ * device current); make that first call outside any stream capture.  The address is
+ * remembered per device ordinal: only the device's primary context (the CUDA runtime's)
+ * is supported.  All calls on a
  * device share the one area and nothing in it has to start at zero (every summary is
  * rewritten before it is read), but two calls whose kernels overlap on the GPU — different
  * streams, no ordering between them — race on it: order them.                          */
@@ -174,7 +184,19 @@ int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size
  * flash_attention_backward_kernel_dkdv (:874-1191, launched :1778-1807), plus the
  * GQA group sum (:1855-1868).  dk/dv are fp32 (B, Skv, Hkv, D) contiguous, already
  * summed over the query heads of each group, as the reference returns them before the
- * context-parallel reduction; dq is in the input dtype with shape.q_strides. */
+ * context-parallel reduction; dq is in the input dtype with its own strides.
+ *
+ * Two schedules produce the gradients:
+ *   fused (default, head_dim 128): one kv-outer kernel computes dK, dV and dQ with five
+ *     matrix products per tile pair; partial dQ tiles are summed into an fp32 accumulator in
+ *     the workspace with bulk reduce-adds (the order of those fp32 additions varies from run
+ *     to run, so dq is reproducible to rounding, not bit for bit) and a last kernel scales
+ *     and casts it;
+ *   two-kernel (KVAX_B200_BWD_TWO_KERNEL in `flags`, and every head_dim the fused kernel does
+ *     not cover): a query-outer dQ kernel and a kv-outer dK/dV kernel, seven products per
+ *     tile pair, bit-reproducible. */
+enum { KVAX_B200_BWD_TWO_KERNEL = 1 };
+
 typedef struct kvax_b200_attn_bwd_params {
   kvax_b200_attn_shape shape;
   const void* q; const void* k; const void* v;
@@ -182,20 +204,34 @@ typedef struct kvax_b200_attn_bwd_params {
   const float* lse;                    /* (B, Hq, Sq) from the forward */
   kvax_b200_block_mask mask_dq;        /* one row per query block */
   kvax_b200_block_mask mask_dkdv;      /* one row per kv block    */
-  void* dq;                            /* (B, Sq, Hq, D) input dtype, strides = q_strides */
+  void* dq;                            /* (B, Sq, Hq, D) input dtype, strides = dq_strides */
   float* dk;                           /* (B, Skv, Hkv, D) fp32 contiguous */
   float* dv;                           /* (B, Skv, Hkv, D) fp32 contiguous */
   int32_t* status;
   /* 0 = everything.  Otherwise a bit set of the parts to launch, for timing or profiling
-     one kernel on a workspace a full call has already filled: 1 tile lists, 2 delta,
-     4 dQ kernel, 8 dK/dV kernel. */
+     one kernel on a workspace a full call has already filled: 1 tile lists, 2 delta (and the
+     zero fill of the dQ accumulator), 4 dQ kernel, 8 dK/dV kernel, 16 fused kernel,
+     32 dQ scale-and-cast.  Bits that do not belong to the chosen schedule are ignored. */
   int32_t stages;
-  int32_t reserved;
+  int32_t flags;                       /* KVAX_B200_BWD_* */
+  int64_t dq_strides[3];               /* element strides (batch, seq, head) of dq */
 } kvax_b200_attn_bwd_params;
 
 size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p);
 int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* workspace, size_t workspace_bytes,
                        kvax_b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Self-test of the bounded device waits.  (No counterpart in the reference.)
+ * Every wait on a barrier inside the attention kernels gives up after a time budget, writes
+ * 100 + barrier id to the status word and lets the kernel run to its end.  This entry point
+ * launches one warp that waits, with the same routine, on a barrier nobody ever arrives on,
+ * with a budget of `budget_ns` (clamped to [1 us, 100 ms]).  Afterwards *status is
+ * 100 + bar_id and *done is 2 ("gave up and returned").  `status` and `done` are int32 words
+ * the device can address (device memory or mapped page-locked host memory), zero on entry.
+ * ---------------------------------------------------------------------------------- */
+int kvax_b200_wait_probe(int32_t* status, int32_t* done, int64_t budget_ns, int32_t bar_id,
+                         kvax_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -21,7 +21,11 @@ EXPORTS = (
     "kvax_b200_attn_fwd",
     "kvax_b200_attn_bwd_workspace_bytes",
     "kvax_b200_attn_bwd",
+    "kvax_b200_wait_probe",
+    "kvax_b200_host_word_device_pointer",
 )
+
+BWD_TWO_KERNEL = 1          # kvax_b200_attn_bwd_params.flags
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -59,7 +63,7 @@ class AttnFwdParams(C.Structure):
 class AttnBwdParams(C.Structure):
     _fields_ = [("shape", AttnShape), ("q", vp), ("k", vp), ("v", vp), ("out", vp), ("dout", vp), ("lse", vp),
                 ("mask_dq", BlockMask), ("mask_dkdv", BlockMask), ("dq", vp), ("dk", vp), ("dv", vp), ("status", vp),
-                ("stages", i32), ("reserved", i32)]
+                ("stages", i32), ("flags", i32), ("dq_strides", i64 * 3)]
 
 
 _lib = None
@@ -98,6 +102,10 @@ def load() -> C.CDLL:
     lib.kvax_b200_attn_bwd_workspace_bytes.argtypes = [C.POINTER(AttnBwdParams)]
     lib.kvax_b200_attn_bwd.restype = C.c_int
     lib.kvax_b200_attn_bwd.argtypes = [C.POINTER(AttnBwdParams), vp, C.c_size_t, vp]
+    lib.kvax_b200_wait_probe.restype = C.c_int
+    lib.kvax_b200_wait_probe.argtypes = [vp, vp, i64, i32, vp]
+    lib.kvax_b200_host_word_device_pointer.restype = C.c_int
+    lib.kvax_b200_host_word_device_pointer.argtypes = [vp, C.POINTER(vp)]
     _lib = lib
     return lib
 

@@ -9,8 +9,10 @@ Differences from the reference: one process per GPU (the context-parallel comman
 under torch.distributed.run and shard the sequence over all ranks), timing with CUDA events
 instead of wall clock, no cuDNN comparator (`--check` compares with a dense torch attention
 on the same GPU when the sequence is short enough to hold the score matrix).  The TFLOP/s
-figure uses the reference's own formula (kvax/utils/math.py:1-30: non-causal FLOPs, divided
-by the number of GPUs), so numbers are comparable with the reference's charts.
+figure uses the reference's own accounting: the dense formula of kvax/utils/math.py:1-30
+(non-causal FLOPs, divided by the number of GPUs) times `calculate_mask_sparsity` of the
+forward mask (forward commands) or of the dq mask (backward commands), as
+kvax/utils/benchmarking.py:423-430 and :565-572 do.
 """
 from __future__ import annotations
 
@@ -85,7 +87,7 @@ def _run(backward, context_parallel, num_iters, batch_size, query_seq_len, kv_se
     import torch.distributed as dist
 
     import kvax_b200 as kv
-    from kvax_b200.ops.mask_creator import print_mask
+    from kvax_b200.ops.mask_creator import calculate_mask_sparsity, print_mask
     from kvax_b200.utils.math import get_multi_head_attention_tflops
 
     if query_seq_len != kv_seq_len and context_parallel:
@@ -146,13 +148,17 @@ def _run(backward, context_parallel, num_iters, batch_size, query_seq_len, kv_se
             qk_head_dim=qk_head_dim, value_head_dim=value_head_dim, causal=False, num_gpus=world,
             forward_pass=True, backward_pass=backward)
         name = "flash_attention_b200" + ("_bwd" if backward else "_fwd") + (f"_cp{world}" if world > 1 else "")
+        out, masks = step()
+        # the reference scales by the sparsity of mask[0] in the forward commands and of mask[1] in the backward ones
+        counted = masks[1] if backward else masks[0]
+        sparsity = calculate_mask_sparsity(counted, params.query_block_size, params.kv_block_size, s_loc, kv_seq_len)
         if rank == 0:
-            msg = f"{name} took {sec * 1e3:.3f} ms per iteration, achieved {tflops_per_iter / sec:.1f} TFLOP/s per GPU"
+            msg = (f"{name} took {sec * 1e3:.3f} ms per iteration, achieved "
+                   f"{tflops_per_iter * sparsity / sec:.1f} TFLOP/s per GPU (mask sparsity {sparsity:.4f})")
             logger.info(msg)
             print(msg, flush=True)
-        out, masks = step()
         if show_attention_mask and rank == 0:
-            print_mask(masks[0])
+            print_mask(masks[0], kv_seq_len // params.kv_block_size)
         if check and world == 1:
             if query_seq_len * kv_seq_len * num_heads * batch_size > (1 << 31):
                 raise click.UsageError("--check holds the dense score matrix: use a shorter sequence")

@@ -48,6 +48,20 @@ int make_tmap(CUtensorMap* map, const void* base, int batch, int seq, int heads,
   return r == CUDA_SUCCESS ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
 
+// fp32 accumulator (batch, seq, heads, D) contiguous; boxes of 32 rows x 32 columns of one head (128-byte rows),
+// 128-byte swizzle: the shared-memory source of the fused backward's reduce-adds.
+int make_tmap_acc(CUtensorMap* map, float* base, int batch, int seq, int heads, int d) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return KVAX_B200_ENODEVICE;
+  cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
+  cuuint64_t gstr[3] = {cuuint64_t(d) * 4, cuuint64_t(heads) * d * 4, cuuint64_t(seq) * heads * d * 4};
+  cuuint32_t box[4] = {32, 1, 32, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
 int check_shape(const kvax_b200_attn_shape& s) {
   if (s.batch <= 0 || s.q_len <= 0 || s.kv_len <= 0 || s.q_heads <= 0 || s.kv_heads <= 0) return KVAX_B200_EINVAL;
   if (s.q_heads % s.kv_heads) return KVAX_B200_EINVAL;
@@ -117,7 +131,12 @@ void fill_list(TileList* l, const ScheduleArgs& sa) {
 
 }  // namespace
 
-extern "C" const char* kvax_b200_version(void) { return "kvax_b200 0.1 (sm_100a)"; }
+extern "C" const char* kvax_b200_version(void) { return "kvax_b200 0.2 (sm_100a)"; }
+
+extern "C" int kvax_b200_host_word_device_pointer(void* host_ptr, void** device_ptr) {
+  if (!host_ptr || !device_ptr) return KVAX_B200_EINVAL;
+  return cudaHostGetDevicePointer(device_ptr, host_ptr, 0) == cudaSuccess ? KVAX_B200_OK : KVAX_B200_EUNSUPPORTED;
+}
 
 extern "C" const char* kvax_b200_error_string(int code) {
   switch (code) {
@@ -184,15 +203,22 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
 
 namespace {
 
-struct BwdLayout { ListLayout dq, dkdv; SummaryLayout sum; size_t delta_off, total; };
+struct BwdLayout { ListLayout dq, dkdv; SummaryLayout sum; size_t delta_off, acc_off, total; bool fused; };
 
-BwdLayout bwd_layout(const kvax_b200_attn_shape& s) {
+bool use_fused(const kvax_b200_attn_bwd_params& p) {
+  return !(p.flags & KVAX_B200_BWD_TWO_KERNEL) && attn_bwd_fused_supports(p.shape.head_dim);
+}
+
+BwdLayout bwd_layout(const kvax_b200_attn_bwd_params& p) {
+  const kvax_b200_attn_shape& s = p.shape;
   BwdLayout l;
+  l.fused = use_fused(p);
   l.dq = list_layout(s.batch, s.q_len, s.kv_len, 0);
   l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total);
   l.sum = summary_layout(s.batch, s.q_len, s.kv_len, l.dkdv.total);
   l.delta_off = l.sum.total;
-  l.total = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));
+  l.acc_off = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));
+  l.total = l.acc_off + (l.fused ? align256(size_t(s.batch) * s.q_len * s.q_heads * s.head_dim * sizeof(float)) : 0);
   return l;
 }
 
@@ -200,7 +226,7 @@ BwdLayout bwd_layout(const kvax_b200_attn_shape& s) {
 
 extern "C" size_t kvax_b200_attn_bwd_workspace_bytes(const kvax_b200_attn_bwd_params* p) {
   if (!p || check_shape(p->shape) != KVAX_B200_OK) return 0;
-  return bwd_layout(p->shape).total;
+  return bwd_layout(*p).total;
 }
 
 extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* workspace, size_t workspace_bytes,
@@ -209,14 +235,18 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   const kvax_b200_attn_shape& s = p->shape;
   int rc = check_shape(s);
   if (rc) return rc;
-  const BwdLayout bl = bwd_layout(s);
+  const BwdLayout bl = bwd_layout(*p);
   if (!workspace || workspace_bytes < bl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
-  if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2] | s.q_strides[0] | s.q_strides[1] | s.q_strides[2]) & 7) return KVAX_B200_EUNSUPPORTED;
+  long long dq_strides[3] = {p->dq_strides[0], p->dq_strides[1], p->dq_strides[2]};
+  if ((dq_strides[0] | dq_strides[1] | dq_strides[2]) == 0)          // not given: dq laid out like q
+    for (int i = 0; i < 3; ++i) dq_strides[i] = s.q_strides[i];
+  if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2] | dq_strides[0] | dq_strides[1] | dq_strides[2]) & 7) return KVAX_B200_EUNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(p->dq) | reinterpret_cast<uintptr_t>(p->dk) | reinterpret_cast<uintptr_t>(p->dv) |
        reinterpret_cast<uintptr_t>(p->out) | reinterpret_cast<uintptr_t>(p->dout)) & 15) return KVAX_B200_EUNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
   float* delta = reinterpret_cast<float*>(ws + bl.delta_off);
+  float* dq_acc = bl.fused ? reinterpret_cast<float*>(ws + bl.acc_off) : nullptr;
   const TokenInfo tok = token_info(s);
 
   MaskView mv_dq, mv_dkdv;
@@ -228,10 +258,11 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   ScheduleArgs sq, sk;
   fill_schedule(&sq, mv_dq, tok, ws, bl.dq, kv_sum, s.q_len, s.kv_len);
   fill_schedule(&sk, mv_dkdv, tok, ws, bl.dkdv, q_sum, s.kv_len, s.q_len);
-  const int stages = p->stages ? p->stages : 15;
+  const int all = bl.fused ? (1 | 2 | 16 | 32) : (1 | 2 | 4 | 8);
+  const int stages = p->stages ? (p->stages & all) : all;
   if (stages & 1) {
     launch_tile_summaries(tok, s.batch, q_sum, kv_sum, st);
-    launch_schedule(false, sq, s.batch, st);
+    if (!bl.fused) launch_schedule(false, sq, s.batch, st);       // the fused kernel only walks the kv-outer lists
     launch_schedule(true, sk, s.batch, st);
   }
   if (cudaGetLastError() != cudaSuccess) return KVAX_B200_ELAUNCH;
@@ -239,10 +270,10 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   long long ostr[3] = {s.o_strides[0], s.o_strides[1], s.o_strides[2]};
   if (stages & 2) {
     rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
-                               ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
+                               dq_acc, ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
     if (rc) return rc;
   }
-  if (!(stages & 12)) return KVAX_B200_OK;
+  if (!(stages & (4 | 8 | 16 | 32))) return KVAX_B200_OK;
 
   CUtensorMap tq, tk, tv, tdo;
   rc = make_tmap(&tq, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);     if (rc) return rc;
@@ -250,19 +281,38 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   rc = make_tmap(&tv, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides);   if (rc) return rc;
   rc = make_tmap(&tdo, p->dout, s.batch, s.q_len, s.q_heads, s.head_dim, s.o_strides); if (rc) return rc;
 
-  BwdLaunch L;
-  BwdArgs& a = L.args;
+  BwdArgs a;
   a.tok = tok; a.lse = p->lse; a.delta = delta;
   a.dq = static_cast<__nv_bfloat16*>(p->dq); a.dk = p->dk; a.dv = p->dv; a.status = p->status;
-  for (int i = 0; i < 3; ++i) a.q_strides[i] = s.q_strides[i];
+  for (int i = 0; i < 3; ++i) a.dq_strides[i] = dq_strides[i];
   a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;
   a.batch = s.batch;
-  L.batch = s.batch; L.head_dim = s.head_dim;
 
+  if (bl.fused) {
+    if (stages & 16) {
+      FusedBwdLaunch F;
+      F.args = a;
+      fill_list(&F.args.list, sk);
+      F.args.mask = mv_dkdv;
+      F.tmap_k = tk; F.tmap_v = tv; F.tmap_q = tq; F.tmap_do = tdo;
+      rc = make_tmap_acc(&F.tmap_dq, dq_acc, s.batch, s.q_len, s.q_heads, s.head_dim);
+      if (rc) return rc;
+      F.batch = s.batch; F.head_dim = s.head_dim;
+      rc = launch_attn_bwd_fused(F, st);
+      if (rc) return rc;
+    }
+    if (stages & 32)
+      return launch_attn_bwd_dq_cast(dq_acc, a.dq, dq_strides, s.batch, s.q_len, s.q_heads, s.head_dim, s.scale, st);
+    return KVAX_B200_OK;
+  }
+
+  BwdLaunch L;
+  L.args = a;
+  L.batch = s.batch; L.head_dim = s.head_dim;
   // dQ: resident Q, dO of one query tile; streams K, V
-  fill_list(&a.list, sq);
-  a.mask = mv_dq;
+  fill_list(&L.args.list, sq);
+  L.args.mask = mv_dq;
   L.tmap_x1 = tq; L.tmap_x2 = tdo; L.tmap_y1 = tk; L.tmap_y2 = tv;
   if (stages & 4) {
     rc = launch_attn_bwd(L, false, st);
@@ -270,8 +320,8 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   }
   if (!(stages & 8)) return KVAX_B200_OK;
   // dK/dV: resident K, V of one kv tile; streams Q, dO of every query head of the group
-  fill_list(&a.list, sk);
-  a.mask = mv_dkdv;
+  fill_list(&L.args.list, sk);
+  L.args.mask = mv_dkdv;
   L.tmap_x1 = tk; L.tmap_x2 = tv; L.tmap_y1 = tq; L.tmap_y2 = tdo;
   return launch_attn_bwd(L, true, st);
 }

@@ -473,7 +473,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int r = qt * kTile + row;
   const bool is_compute = tid < kComputeThreads;
   const bool row_valid = is_compute && (r < a.tok.q_len);
-  __nv_bfloat16* dq_row = a.dq + (long long)b * a.q_strides[0] + (long long)r * a.q_strides[1] + (long long)h * a.q_strides[2] + half * (D / 2);
+  __nv_bfloat16* dq_row = a.dq + (long long)b * a.dq_strides[0] + (long long)r * a.dq_strides[1] + (long long)h * a.dq_strides[2] + half * (D / 2);
 
   if (n_items == 0) {
     if (row_valid) {
@@ -709,12 +709,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 // delta[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]   (fp32), HBM-bound.
-// D/8 lanes per row (16-byte loads), 32 / (D/8) rows per warp.
+// D/8 lanes per row (16-byte loads), 32 / (D/8) rows per warp.  With `dq_acc` the same lanes zero
+// their eight elements of the row's fp32 dQ accumulator ((B, Sq, Hq, D) contiguous).
 template <int D>
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                                             const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                                                            long long sb, long long ss, long long sh, int batch, int seq,
-                                                            int heads) {
+                                                            float* __restrict__ dq_acc, long long sb, long long ss,
+                                                            long long sh, int batch, int seq, int heads) {
   constexpr int kLanes = D / 8, kRowsPerWarp = 32 / kLanes;
   const int lane = threadIdx.x & 31;
   const int sub = lane / kLanes, li = lane % kLanes;
@@ -729,6 +730,11 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
       const long long off = b * sb + s * ss + h * sh + li * 8;
       const uint4 x = __ldg(reinterpret_cast<const uint4*>(o + off));
       const uint4 y = __ldg(reinterpret_cast<const uint4*>(d_o + off));
+      if (dq_acc) {
+        float4* z = reinterpret_cast<float4*>(dq_acc + row * D + li * 8);
+        z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
       const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
 #pragma unroll
@@ -772,16 +778,16 @@ int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream) {
   return KVAX_B200_EUNSUPPORTED;
 }
 
-int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, const long long* strides,
-                          int batch, int seq, int heads, int head_dim, cudaStream_t stream) {
+int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, float* dq_acc,
+                          const long long* strides, int batch, int seq, int heads, int head_dim, cudaStream_t stream) {
   const long long rows = (long long)batch * seq * heads;
   const int rows_per_warp = 32 / (head_dim / 8);
   long long blocks = (rows / rows_per_warp + 7) / 8 + 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (head_dim == 128)
-    attn_bwd_delta_kernel<128><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, strides[0], strides[1], strides[2], batch, seq, heads);
+    attn_bwd_delta_kernel<128><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads);
   else if (head_dim == 64)
-    attn_bwd_delta_kernel<64><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, strides[0], strides[1], strides[2], batch, seq, heads);
+    attn_bwd_delta_kernel<64><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads);
   else
     return KVAX_B200_EUNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;

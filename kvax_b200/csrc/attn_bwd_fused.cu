@@ -1,0 +1,580 @@
+// Fused flash-attention backward for sm_100a (B200): dK, dV and dQ from ONE kv-outer kernel,
+// five matrix products per tile pair (S, dP, dV, dK, dQ) and one exponential per score, instead
+// of the seven products and two exponentials of the dQ kernel + dK/dV kernel pair in attn_bwd.cu.
+//
+// CTA = (128-row kv tile, kv head, batch); K and V of the tile stay in shared memory; the Q and dO
+// tiles of every query head of the GQA group x every listed query tile stream through a two-stage
+// TMA ring.  Fourteen warps:
+//   warps 0-7   register math.  Thread t owns kv row t % 128 (= TMEM lane) and the 64-column half
+//               t / 128 of every 128 x 128 tile:
+//                 A: P^T = exp2(S^T * scale*log2e - LSE2), masked, -> bf16 -> TMEM (over S^T)
+//                 B: dS^T = P^T * (dP^T - delta) -> bf16 -> shared memory, into the slot of dO(i),
+//                    which is dead once dV(i) has run; written in the 128-byte-swizzled layout TMA
+//                    produces, so the one copy serves as K-major A operand of dK and as MN-major A
+//                    operand of dQ.
+//   warps 8-11  dQ drain.  Warp w owns TMEM lanes 32 (w % 4) ...: it pulls the finished 128 x D fp32
+//               dQ tile out of TMEM (freeing the columns for the next dP at once), stages it through a
+//               private double-buffered 4 KB area and adds it to the fp32 dQ accumulator in global
+//               memory with TMA tile reduce-adds (cp.reduce.async.bulk.tensor, this GPU's own memory,
+//               no multicast) -- asynchronously, while the register-math warps work on the next item.
+//   warp 12     TMA producer (K, V once; per item Q, dO and the 128 LSE2 / delta values of the query
+//               tile) and TMEM allocation.
+//   warp 13     MMA issuer (whole warp runs the loop, one elected lane issues):
+//                 S^T(0) dP^T(0) | dV(i) S^T(i+1) | dQ(i) dK(i) | dP^T(i+1) | ...
+//               S^T  = K Q^T        (SS)            -> T1
+//               dP^T = V dO^T       (SS)            -> T2
+//               dV  += P^T dO       (A = P^T in TMEM over T1, B = dO N-major)
+//               dQ   = dS K         (A = dS^T tile read MN-major, B = K tile read MN-major) -> T2, over dP^T
+//               dK  += dS^T Q       (A = dS^T tile read K-major,  B = Q N-major)
+// TMEM (512 columns): T1 | T2 | dV | dK.  dQ shares its columns with dP^T: that makes
+// dP^T(i) -> dS^T(i) -> dQ(i) -> drain -> dP^T(i+1) one serial chain, which the other chain
+// S^T(i+1) -> P^T(i+1) -> dV(i+1) overlaps.
+// Shared memory (D = 128): K, V 64 KB + 2 x (Q, dO) 128 KB + drain staging 32 KB + LSE2/delta 2 KB.
+//
+// dQ is accumulated with fp32 atomics at L2, so its summation order (and last bits) vary from run
+// to run; dK and dV are accumulated in TMEM in a fixed order.
+//
+// Semantics follow flash_attention_backward_kernel_dquery (kvax/ops/flash_attention_triton.py:620-871)
+// and flash_attention_backward_kernel_dkdv (:874-1191); the element mask of partial tiles is the
+// kv-outer rule of :1067-1167.
+#include <cuda_runtime.h>
+
+#include "attn_common.cuh"
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace kvx {
+
+namespace {
+
+constexpr int kTmemCols = 512;
+constexpr int kComputeWarps = 8;
+constexpr int kComputeThreads = kComputeWarps * 32;
+constexpr int kDrainWarp0 = kComputeWarps;             // 8 % 4 == 0: drain warp w owns TMEM lane quarter w % 4
+constexpr int kDrainWarps = 4;
+constexpr int kProducerWarp = kDrainWarp0 + kDrainWarps, kMmaWarp = kProducerWarp + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;          // 448
+constexpr int kSlice = kTile / 2;                      // columns per register-math thread
+constexpr int kStageBuf = 32 * 32 * 4;                 // one drain staging buffer: 32 rows x 32 fp32
+
+enum FBar { F_XFULL = 0, F_YFULL0, F_YFULL1, F_YEMPTY0, F_YEMPTY1, F_SFULL, F_PFULL, F_DPFULL, F_DVDONE, F_DSFULL,
+            F_DQFULL, F_DRAINED, F_ACCFULL, F_COUNT };
+
+template <int D>
+struct FusedSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kBoxBytes = kTile * 64 * 2;
+  static constexpr int kX1 = 0, kX2 = kTileBytes;
+  static constexpr int kY = 2 * kTileBytes;                       // stage s: Q at kY + s*2*tile, dO (later dS^T) right after
+  static constexpr int kStage = 6 * kTileBytes;                   // drain warp w, buffer u: kStage + (2 w + u) * kStageBuf
+  static constexpr int kCols = kStage + kDrainWarps * 2 * kStageBuf;   // stage s: lse2[128] | delta[128]
+  static constexpr int kColBytes = kTile * 4;
+  static constexpr int kBars = kCols + 2 * 2 * kColBytes;
+  static constexpr int kTmemSlot = kBars + 8 * F_COUNT;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                      const __grid_constant__ CUtensorMap tmap_dq, const BwdArgs a) {
+  using L = FusedSmem<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbort);
+  float* s_cols = reinterpret_cast<float*>(smem + L::kCols);
+
+  // The swizzled tiles need a 1024-byte aligned base and the layout leaves no slack to round up.
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) report_status(a.status, ST_SMEM_MISALIGNED);
+    return;
+  }
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int row_rank, kvh;
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.kv_heads, &row_rank, &kvh);
+  const long long list_row = __ldg(a.list.order + row_rank);     // longest lists first
+  const int b = int(list_row / a.list.n_outer_tiles), kt = int(list_row % a.list.n_outer_tiles);
+  const int group = a.group;
+  const int count = __ldg(a.list.counts + list_row);
+  const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
+  const int n_items = count * group;           // item i: query head kvh*group + i / count, query tile list[i % count]
+  const int q_len = a.tok.q_len;
+
+  const int row = tid & (kTile - 1);           // kv row / TMEM lane of a register-math thread
+  const int half = (tid >> 7) & 1;             // its column half; in the epilogue its half of the D columns
+  const int r = kt * kTile + row;
+  const bool is_compute = tid < kComputeThreads;
+  const bool row_valid = is_compute && (r < a.tok.kv_len);
+  float* dk_row = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
+  float* dv_row = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
+
+  if (n_items == 0) {                          // no contributing tile: zero gradients
+    if (row_valid) {
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { reinterpret_cast<float4*>(dk_row)[i] = z; reinterpret_cast<float4*>(dv_row)[i] = z; }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int i = 0; i < F_COUNT; ++i) {
+      const int n = (i == F_PFULL || i == F_DSFULL) ? kComputeThreads : (i == F_DRAINED ? kDrainWarps * 32 : 1);
+      mbar_init(&bars[i], n);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tT1 = tmem_base, tT2 = tmem_base + kTile;
+  const uint32_t tDV = tmem_base + 2 * kTile, tDK = tmem_base + 2 * kTile + D;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer (whole warp; one elected lane issues)
+    const int n = __shfl_sync(0xffffffffu, n_items, 0);
+    const int cnt = __shfl_sync(0xffffffffu, count, 0);
+    if (elect_one()) {
+      prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_do);
+      mbar_arrive_expect_tx(&bars[F_XFULL], 2 * L::kTileBytes);
+#pragma unroll
+      for (int x = 0; x < D / 64; ++x) {
+        tma_load_4d(smem + L::kX1 + x * L::kBoxBytes, &tmap_k, &bars[F_XFULL], x * 64, kvh, kt * kTile, b);
+        tma_load_4d(smem + L::kX2 + x * L::kBoxBytes, &tmap_v, &bars[F_XFULL], x * 64, kvh, kt * kTile, b);
+      }
+    }
+    __syncwarp();
+    bool ok = true;
+    uint32_t e_next = __ldg(list);                 // list entries are fetched one iteration ahead
+    int li = 0, qh = kvh * group;                  // index into the list, query head
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i & 1;
+      const int u = int(e_next & ~kPartialBit);
+      const int yh = qh;
+      if (++li == cnt) { li = 0; ++qh; }
+      if (i + 1 < n) e_next = __ldg(list + li);
+      if (i >= 2) {
+        ok = mbar_wait(&bars[F_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, F_YEMPTY0 + st);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (!ok) break;
+      uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
+      uint8_t* y2 = y1 + L::kTileBytes;
+      float* cs = s_cols + st * 2 * kTile;
+      const int col0 = u * kTile;
+      const float* lse_src = a.lse + ((long long)b * a.q_heads + yh) * q_len + col0;
+      const float* dl_src = a.delta + ((long long)b * a.q_heads + yh) * q_len + col0;
+      const bool bulk = (col0 + kTile <= q_len) &&
+                        (((reinterpret_cast<uintptr_t>(lse_src) | reinterpret_cast<uintptr_t>(dl_src)) & 15) == 0);
+      if (!bulk) {                                 // tile cut by the end of the sequence, or unaligned rows
+#pragma unroll
+        for (int k = 0; k < kTile / 32; ++k) {
+          const int j = lane + 32 * k;
+          const bool valid = col0 + j < q_len;
+          cs[j] = valid ? __ldg(lse_src + j) : INFINITY;            // exp2(-inf) = 0
+          cs[kTile + j] = valid ? __ldg(dl_src + j) : 0.f;
+        }
+        fence_proxy_async_smem();
+      }
+      __syncwarp();
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&bars[F_YFULL0 + st], 2 * L::kTileBytes + (bulk ? 2 * L::kColBytes : 0));
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x) {
+          tma_load_4d(y1 + x * L::kBoxBytes, &tmap_q, &bars[F_YFULL0 + st], x * 64, yh, u * kTile, b);
+          tma_load_4d(y2 + x * L::kBoxBytes, &tmap_do, &bars[F_YFULL0 + st], x * 64, yh, u * kTile, b);
+        }
+        if (bulk) {
+          bulk_load_1d(cs, lse_src, L::kColBytes, &bars[F_YFULL0 + st]);
+          bulk_load_1d(cs + kTile, dl_src, L::kColBytes, &bars[F_YFULL0 + st]);
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
+    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);    // X (K-major) x Y (K-major)
+    constexpr uint32_t idesc_dv = make_idesc_bf16(kTile, D, 0, 1);       // P^T (TMEM) x dO (N-major)
+    constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, 1, 1);       // dS^T tile (MN-major A) x K tile (MN-major B)
+    constexpr uint32_t idesc_dk = make_idesc_bf16(kTile, D, 0, 1);       // dS^T tile (K-major A) x Q (N-major B)
+    const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
+    const uint32_t kmn_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), L::kBoxBytes);   // K tile with kv as the contraction index
+    const uint32_t ybase = smem_u32(smem + L::kY);
+    const int n = __shfl_sync(0xffffffffu, n_items, 0);
+    bool ok = true;
+    // `tmem_sync`: the barrier orders TMEM loads / stores of other threads before the MMAs that follow; barriers
+    // completed by TMA alone need no tcgen05 fence.
+    auto wait = [&](int bar, uint32_t parity, bool tmem_sync) {
+      ok = mbar_wait(&bars[bar], parity, abort_flag, a.status, bar);
+      ok = __all_sync(0xffffffffu, ok);
+      if (tmem_sync) tc_fence_after();
+    };
+    auto issue_t = [&](uint32_t t_addr, uint32_t x_lo, uint32_t y_lo) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;
+        umma_ss_lo(t_addr, x_lo + off, y_lo + off, idesc_t, kk > 0);
+      }
+    };
+    wait(F_XFULL, 0, false);
+    if (ok) wait(F_YFULL0, 0, false);
+    if (ok) {
+      if (elect_one()) {
+        issue_t(tT1, x1_lo, sdesc_lo_sw128(ybase, 16));
+        umma_commit(&bars[F_SFULL]);
+        issue_t(tT2, x2_lo, sdesc_lo_sw128(ybase + L::kTileBytes, 16));
+        umma_commit(&bars[F_DPFULL]);
+      }
+      __syncwarp();
+    }
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = uint32_t(i & 1);
+      const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
+      const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
+      const uint32_t acc_on = (i > 0) ? 1u : 0u;
+      const bool more = (i + 1 < n);
+      wait(F_PFULL, ph, true);                                                      // P^T(i) written, S^T(i) consumed
+      if (!ok) break;
+      if (elect_one()) {
+        // dV += P^T dO: the half h of the register-math threads wrote its four K-steps at column offset 64 h
+        const uint32_t do_lo = sdesc_lo_sw128(y2, L::kBoxBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts_lo(tDV, tT1 + (kk >> 2) * kSlice + (kk & 3) * 8, do_lo + ((kk * 16 * 128) >> 4), idesc_dv, acc_on | (kk > 0));
+        umma_commit(&bars[F_DVDONE]);                                               // the dO slot may now take dS^T
+      }
+      __syncwarp();
+      if (more) {
+        wait(F_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
+        if (!ok) break;
+        if (elect_one()) {
+          issue_t(tT1, x1_lo, sdesc_lo_sw128(y1n, 16));                             // scores of item i+1
+          umma_commit(&bars[F_SFULL]);
+        }
+        __syncwarp();
+      }
+      wait(F_DSFULL, ph, true);                                                     // dS^T(i) in the dO slot, dP^T(i) consumed
+      if (!ok) break;
+      if (elect_one()) {
+        // dQ(i) = dS K over the dP^T columns: both operands read with kv as the contraction index (16 kv rows per
+        // step = 16 lines of 128 bytes)
+        const uint32_t ds_mn_lo = sdesc_lo_sw128(y2, L::kBoxBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ss_lo(tT2, ds_mn_lo + ((kk * 16 * 128) >> 4), kmn_lo + ((kk * 16 * 128) >> 4), idesc_dq, kk > 0);
+        umma_commit(&bars[F_DQFULL]);
+        // dK(i) += dS^T(i) Q(i)
+        const uint32_t ds_k_lo = sdesc_lo_sw128(y2, 16);
+        const uint32_t q_lo = sdesc_lo_sw128(y1, L::kBoxBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;
+          umma_ss_lo(tDK, ds_k_lo + off, q_lo + ((kk * 16 * 128) >> 4), idesc_dk, acc_on | (kk > 0));
+        }
+        umma_commit(&bars[F_YEMPTY0 + st]);
+        if (!more) umma_commit(&bars[F_ACCFULL]);
+      }
+      __syncwarp();
+      if (more) {
+        wait(F_DRAINED, ph, true);                                                  // dQ(i) has left the T2 columns
+        if (!ok) break;
+        if (elect_one()) {
+          issue_t(tT2, x2_lo, sdesc_lo_sw128(y2n, 16));                             // dP^T of item i+1
+          umma_commit(&bars[F_DPFULL]);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (is_compute) {
+    // ------------------------------------------------------------------ register math
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const int cb = half * kSlice;                             // first column (within the tile) of this thread
+    const uint32_t my_t1 = tT1 + lane_base + cb;              // fp32 columns of this thread; P^T goes to the first 32 of them
+    const uint32_t my_t2 = tT2 + lane_base + cb;
+    const float c = a.scale_log2e;
+    const RowBounds rb = load_bounds(a.mask, b, min(r, a.tok.kv_len - 1));
+    int kv_seg = KVAX_B200_PADDING_SEGMENT_ID, kv_pos = 0;
+    if (row_valid) {
+      kv_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
+      kv_pos = a.tok.sequential ? r : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + r);
+    }
+    const int32_t* q_seg = a.tok.q_seg + (long long)b * q_len;
+    const int32_t* q_pos = a.tok.sequential ? nullptr : a.tok.q_pos + (long long)b * q_len;
+    const int second_from = (q_len + 1) >> 1;                 // first local query of the second half (2 r >= q_len)
+
+    // Mask bits of this kv row for the 32 queries [i0, i0 + 32).  With assume_sequential_positions the query
+    // position is its index plus the global offset of its half of the local queries, which is folded into the
+    // kv position so that the index itself can be compared.
+    auto chunk_keep = [&](int i0) -> uint32_t {
+      if (!a.tok.sequential) return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos, q_seg + i0, q_pos + i0);
+      if (i0 >= second_from || i0 + 32 <= second_from || a.tok.off_first == a.tok.off_second) {
+        const int off = (i0 >= second_from) ? a.tok.off_second : a.tok.off_first;
+        return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos - off, q_seg + i0, nullptr);
+      }
+      uint32_t bits = 0;                                      // the chunk straddles the two halves
+      if (row_valid) {
+        for (int j = 0; j < 32; ++j) {
+          const int i = i0 + j;
+          if (i < q_len) {
+            const int p = i + (i >= second_from ? a.tok.off_second : a.tok.off_first);
+            bits |= (element_allowed<true>(rb, i, __ldg(q_seg + i) == kv_seg, p >= kv_pos) ? 1u : 0u) << j;
+          }
+        }
+      }
+      return bits;
+    };
+
+    bool ok = true;
+    uint32_t e_next = __ldg(list);
+    int li = 0;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const uint32_t e = e_next;
+      if (++li == count) li = 0;
+      if (i + 1 < n_items) e_next = __ldg(list + li);
+      const int c0 = int(e & ~kPartialBit) * kTile;
+      const bool partial = (e & kPartialBit) != 0;
+      const int st = i & 1;
+      const uint32_t ph = uint32_t(i & 1);
+      const float* cs = s_cols + st * 2 * kTile;
+      const float4* cs_lse = reinterpret_cast<const float4*>(cs + cb);
+      const float4* cs_dl = reinterpret_cast<const float4*>(cs + kTile + cb);
+
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
+      if (partial) { keep[0] = chunk_keep(c0 + cb); keep[1] = chunk_keep(c0 + cb + 32); }
+
+      // LSE2 / delta of this item have landed together with its Q and dO tiles
+      ok = mbar_wait(&bars[F_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, F_YFULL0 + st);
+      if (!ok) break;
+
+      // ---- A: P^T = exp2(S^T * scale*log2e - LSE2); the 64 values of this thread stay in registers for B
+      ok = mbar_wait(&bars[F_SFULL], ph, abort_flag, a.status, F_SFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[2][32];
+      tmem_ld32(my_t1, v[0]);
+      tmem_ld32(my_t1 + 32, v[1]);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        tmem_ld_wait(v[ch]);
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 4) {
+          const float4 ls = cs_lse[(ch * 32 + jj) >> 2];
+          const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float pv = fast_exp2(fmaf(__uint_as_float(v[ch][jj + t]), c, -l4[t]));
+            if (partial) pv = ((keep[ch] >> (jj + t)) & 1u) ? pv : 0.f;
+            v[ch][jj + t] = __float_as_uint(pv);
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
+        tmem_st16(my_t1 + ch * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[F_PFULL]);
+
+      // ---- B: dS^T = P^T * (dP^T - delta) -> bf16 -> the shared-memory slot of dO(i), dead once dV(i) has run
+      ok = mbar_wait(&bars[F_DPFULL], ph, abort_flag, a.status, F_DPFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dp[2][16];                                     // 16 columns at a time, the next request in flight
+      tmem_ld16(my_t2, dp[0]);
+      ok = mbar_wait(&bars[F_DVDONE], ph, abort_flag, a.status, F_DVDONE);
+      if (!ok) break;
+      {
+        // kv row `row`, queries [64 half, 64 half + 64) = one 128-byte row of box `half`: eight 16-byte chunks at the
+        // positions the 128-byte swizzle assigns them
+        uint8_t* slot = smem + L::kY + st * 2 * L::kTileBytes + L::kTileBytes + half * L::kBoxBytes + row * 128;
+#pragma unroll
+        for (int sc = 0; sc < 4; ++sc) {                      // columns [16 sc, 16 sc + 16) of this thread's 64
+          if (sc + 1 < 4) tmem_ld16(my_t2 + (sc + 1) * 16, dp[(sc + 1) & 1]);
+          tmem_ld_wait16(dp[sc & 1]);
+          const int ch = sc >> 1, j0 = (sc & 1) * 16;
+#pragma unroll
+          for (int jj = 0; jj < 16; jj += 8) {
+            const float4 dl0 = cs_dl[(sc * 16 + jj) >> 2], dl1 = cs_dl[((sc * 16 + jj) >> 2) + 1];
+            const float dl[8] = {dl0.x, dl0.y, dl0.z, dl0.w, dl1.x, dl1.y, dl1.z, dl1.w};
+            float d[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+              d[t] = __uint_as_float(v[ch][j0 + jj + t]) * (__uint_as_float(dp[sc & 1][jj + t]) - dl[t]);
+            const int ck = sc * 2 + (jj >> 3);                // 16-byte chunk: 8 queries
+            *reinterpret_cast<uint4*>(slot + ((ck ^ (row & 7)) << 4)) =
+                make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars[F_DSFULL]);
+    }
+
+    if (ok) ok = mbar_wait(&bars[F_ACCFULL], 0, abort_flag, a.status, F_ACCFULL);
+    if (ok) {
+      tc_fence_after();
+      // every thread stores D/2 columns of its row: columns [half*D/2, (half+1)*D/2)
+#pragma unroll
+      for (int ch = 0; ch < D / 64; ++ch) {
+        uint32_t v1[32], v2[32];
+        tmem_ld32(tDV + lane_base + half * (D / 2) + ch * 32, v1);
+        tmem_ld32(tDK + lane_base + half * (D / 2) + ch * 32, v2);
+        tmem_ld_wait(v1);
+        tmem_ld_wait(v2);
+        if (row_valid) {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 4) {
+            reinterpret_cast<float4*>(dv_row)[(ch * 32 + jj) >> 2] =
+                make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
+            reinterpret_cast<float4*>(dk_row)[(ch * 32 + jj) >> 2] =
+                make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
+                            __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ drain (warps 8-11)
+    const int dw = warp - kDrainWarp0;                        // = TMEM lane quarter of this warp
+    const uint32_t lane_base = uint32_t(dw * 32) << 16;
+    uint8_t* stage = smem + L::kStage + dw * 2 * kStageBuf;
+    if (lane == 0) prefetch_tmap(&tmap_dq);
+    bool ok = true;
+    uint32_t e_next = __ldg(list);
+    int li = 0, qh = kvh * group;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const int q0 = int(e_next & ~kPartialBit) * kTile + dw * 32;    // first query row this warp drains
+      const int yh = qh;
+      if (++li == count) { li = 0; ++qh; }
+      if (i + 1 < n_items) e_next = __ldg(list + li);
+      ok = mbar_wait(&bars[F_DQFULL], uint32_t(i & 1), abort_flag, a.status, F_DQFULL);
+      if (!ok) break;
+      tc_fence_after();
+      // Registers hold three 32-column chunks at a time (the register file leaves 128 per thread): chunks 0-2 are
+      // requested at once, chunk 0 goes to its staging buffer as soon as it arrives, its registers take chunk 3, and
+      // the T2 columns are released as soon as the last chunk is in registers.
+      const bool live = q0 < q_len;                           // rows beyond the sequence are clipped by TMA; skip all-out boxes
+      auto stage_out = [&](int ch, const uint32_t (&x)[32]) {
+        if (!live) return;
+        uint8_t* buf = stage + (ch & 1) * kStageBuf;
+        if (lane == 0) bulk_wait_group_read<1>();             // the reduce-add issued from this buffer two rounds ago has read it
+        __syncwarp();
+        uint8_t* dst = buf + lane * 128;                      // query row q0 + lane: 32 fp32 = 128 bytes, swizzled
+#pragma unroll
+        for (int ck = 0; ck < 8; ++ck)
+          *reinterpret_cast<uint4*>(dst + ((ck ^ (lane & 7)) << 4)) = make_uint4(x[4 * ck], x[4 * ck + 1], x[4 * ck + 2], x[4 * ck + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_4d(&tmap_dq, buf, ch * 32, yh, q0, b);
+          bulk_commit_group();
+        }
+      };
+      static_assert(D == 128 || D == 64, "drain schedule written for two or four 32-column chunks");
+      if (D == 128) {
+        uint32_t x0[32], x1[32], x2[32];
+        tmem_ld32(tT2 + lane_base, x0);
+        tmem_ld32(tT2 + lane_base + 32, x1);
+        tmem_ld32(tT2 + lane_base + 64, x2);
+        tmem_ld_wait(x0);
+        stage_out(0, x0);
+        tmem_ld32(tT2 + lane_base + 96, x0);
+        tmem_ld_wait(x1);
+        tmem_ld_wait(x2);
+        tmem_ld_wait(x0);
+        tc_fence_before();
+        mbar_arrive(&bars[F_DRAINED]);                        // the T2 columns may take dP^T(i+1)
+        stage_out(1, x1);
+        stage_out(2, x2);
+        stage_out(3, x0);
+      } else {
+        uint32_t x0[32], x1[32];
+        tmem_ld32(tT2 + lane_base, x0);
+        tmem_ld32(tT2 + lane_base + 32, x1);
+        tmem_ld_wait(x0);
+        tmem_ld_wait(x1);
+        tc_fence_before();
+        mbar_arrive(&bars[F_DRAINED]);
+        stage_out(0, x0);
+        stage_out(1, x1);
+      }
+    }
+    if (lane == 0) bulk_wait_group<0>();                      // all reduce-adds performed before the CTA goes away
+    __syncwarp();
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) {
+    // After an aborted run a TMA copy may still be in flight: give it a bounded moment
+    // before the CTA (and its shared memory) goes away.
+    if (*abort_flag && lane == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) { }
+    }
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// dq[b, s, h, :] = bf16(scale * acc[b, s, h, :]); acc is (B, Sq, Hq, D) fp32 contiguous, dq has its own strides.
+__global__ void __launch_bounds__(256) attn_bwd_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                              long long s0, long long s1, long long s2, int seq, int heads, int dim,
+                                                              float scale, long long n_vec) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 8;
+    const int d = int(e % dim);
+    const long long t = e / dim;
+    const int h = int(t % heads);
+    const long long t2 = t / heads;
+    const int s = int(t2 % seq);
+    const long long b = t2 / seq;
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(acc + e)), y = __ldcs(reinterpret_cast<const float4*>(acc + e) + 1);
+    uint4 w;
+    w.x = pack_bf16(x.x * scale, x.y * scale); w.y = pack_bf16(x.z * scale, x.w * scale);
+    w.z = pack_bf16(y.x * scale, y.y * scale); w.w = pack_bf16(y.z * scale, y.w * scale);
+    *reinterpret_cast<uint4*>(dq + b * s0 + s * s1 + h * s2 + d) = w;
+  }
+}
+
+template <int D>
+int launch_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
+  constexpr int smem = FusedSmem<D>::kTotal;
+  auto kern = attn_bwd_fused_kernel<D>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
+  dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_k, L.tmap_v, L.tmap_q, L.tmap_do, L.tmap_dq, L.args);
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
+}  // namespace
+
+bool attn_bwd_fused_supports(int head_dim) { return head_dim == 128; }
+
+int launch_attn_bwd_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
+  if (L.head_dim == 128) return launch_fused<128>(L, stream);
+  return KVAX_B200_EUNSUPPORTED;
+}
+
+int launch_attn_bwd_dq_cast(const float* acc, __nv_bfloat16* dq, const long long* dq_strides, int batch, int seq, int heads,
+                            int dim, float scale, cudaStream_t stream) {
+  const long long n_vec = (long long)batch * seq * heads * dim / 8;
+  const long long want = (n_vec + 255) / 256;
+  const int blocks = int(want < 148 * 16 ? (want > 0 ? want : 1) : 148 * 16);
+  attn_bwd_dq_cast_kernel<<<blocks, 256, 0, stream>>>(acc, dq, dq_strides[0], dq_strides[1], dq_strides[2], seq, heads, dim, scale, n_vec);
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
+}  // namespace kvx

@@ -52,7 +52,7 @@ struct BwdArgs {
   float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) fp32 contiguous
   float* dv;
   int32_t* status;
-  long long q_strides[3];
+  long long dq_strides[3];  // element strides (batch, seq, head) of dq
   float scale_log2e, scale;
   int32_t q_heads, kv_heads, group;
   int32_t batch;
@@ -64,7 +64,21 @@ struct BwdLaunch {
   int batch, head_dim;
 };
 int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream);
-int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, const long long* strides,
-                          int batch, int seq, int heads, int head_dim, cudaStream_t stream);
+// delta = rowsum(O * dO); when `dq_acc` is given, the (B, Sq, Hq, D) fp32 dQ accumulator of the fused
+// backward is zero-filled by the same pass.
+int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, float* dq_acc,
+                          const long long* strides, int batch, int seq, int heads, int head_dim, cudaStream_t stream);
+
+// Fused backward (attn_bwd_fused.cu): K, V, Q, dO tensor maps as for the dK/dV kernel plus the map of the
+// fp32 dQ accumulator (B, Sq, Hq, D), boxes of 32 rows x 32 columns, 128-byte swizzle.
+struct FusedBwdLaunch {
+  CUtensorMap tmap_k, tmap_v, tmap_q, tmap_do, tmap_dq;
+  BwdArgs args;             // list / mask: the kv-outer ones
+  int batch, head_dim;
+};
+bool attn_bwd_fused_supports(int head_dim);
+int launch_attn_bwd_fused(const FusedBwdLaunch& L, cudaStream_t stream);
+int launch_attn_bwd_dq_cast(const float* acc, __nv_bfloat16* dq, const long long* dq_strides, int batch, int seq, int heads,
+                            int dim, float scale, cudaStream_t stream);
 
 }  // namespace kvx

@@ -185,7 +185,7 @@ extern "C" int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* worksp
   if (p->batch <= 0 || p->q_len <= 0 || p->kv_len <= 0 || p->n_masks < 1 || p->n_masks > 3) return KVAX_B200_EINVAL;
   const size_t need = kvax_b200_mask_workspace_bytes(p);
   if (need == 0) return KVAX_B200_EINVAL;
-  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return KVAX_B200_EWORKSPACE;
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
 
   SummaryArgs sa{};
   BoundsArgs ba{};
@@ -237,13 +237,16 @@ static __device__ __align__(256) unsigned char g_mask_scratch[kStaticScratchByte
 
 // Device address of g_mask_scratch per device.  In host code the symbol's name is only a
 // stand-in; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
-// device while that device is current.
+// device while that device is current.  The cache is keyed by device ordinal, i.e. it
+// assumes the device's primary context (the one the CUDA runtime uses).
 void* g_scratch_addr[kMaxDevices] = {};
 
 }  // namespace
 
 extern "C" int kvax_b200_mask_build_static(const kvax_b200_mask_params* p, kvax_b200_stream_t stream) {
-  if (!p) return KVAX_B200_EINVAL;
+  // arguments first: a size computed from a non-positive batch or length means nothing
+  if (!p || !p->q_positions || !p->q_segment_ids || !p->kv_positions || !p->kv_segment_ids) return KVAX_B200_EINVAL;
+  if (p->batch <= 0 || p->q_len <= 0 || p->kv_len <= 0 || p->n_masks < 1 || p->n_masks > 3) return KVAX_B200_EINVAL;
   const size_t need = kvax_b200_mask_workspace_bytes(p);
   if (need == 0) return KVAX_B200_EINVAL;
   if (need > kStaticScratchBytes) return KVAX_B200_ESCRATCH;

@@ -13,6 +13,7 @@ namespace kvx {
 // ---------------------------------------------------------------------------
 enum : int {
   ST_OK = 0,
+  ST_SMEM_MISALIGNED = 90, // the dynamic shared memory window does not start on a 1024-byte boundary
   ST_WAIT_TIMEOUT = 100,   // + barrier id: a bounded mbarrier wait gave up
 };
 
@@ -59,10 +60,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // protocol error; the waiter then records a status code and every role leaves its loop.
 constexpr uint64_t kWaitBudgetNs = 2000ull * 1000ull * 1000ull;
 
+// Records a device-side failure in the launch's status word: the first code written stays.
+// The word may live in device memory or in page-locked host memory that the device can
+// address (so that the host can look at it without synchronising); plain volatile accesses
+// work on both, and two CTAs failing at once may both write, which is harmless.
+__device__ __forceinline__ void report_status(int* status, int code) {
+  if (!status) return;
+  volatile int* s = status;
+  if (*s == 0) *s = code;
+}
+
 // Bounded wait.  Returns false when it gave up (status word set, *abort_flag raised) or
 // when another thread had already raised *abort_flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int bar_id) {
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                 int* status, int bar_id, uint64_t budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -70,13 +81,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, 0, ST_WAIT_TIMEOUT + bar_id);
+        report_status(status, ST_WAIT_TIMEOUT + bar_id);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int bar_id) {
+  return mbar_wait_budget(bar, parity, abort_flag, status, bar_id, kWaitBudgetNs);
 }
 
 // Read-only global load that stays where it is written.  The kernels fetch the next tile-list
@@ -109,6 +124,31 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
+}
+// Tile reduce-add from this CTA's shared memory into this GPU's global memory (element type and
+// swizzle come from the tensor map).  Completion is tracked by the issuing thread's bulk groups.
+// Never start one at a negative coordinate; rows beyond the tensor's extent are clipped.
+__device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, const void* smem_src, int c0, int c1, int c2,
+                                                  int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are incomplete (writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
@@ -245,6 +285,23 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                  "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
                  "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
                  "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                :
                : "memory");
 }

@@ -1,4 +1,13 @@
-from kvax_b200.ops.flash_attention import flash_attention, get_context_parallel_mode, set_context_parallel_mode
-from kvax_b200.ops.mask_creator import create_attention_mask
+from kvax_b200._status import check_last_status, last_status
+from kvax_b200.ops.flash_attention import (
+    flash_attention,
+    get_backward_mode,
+    get_context_parallel_mode,
+    set_backward_mode,
+    set_context_parallel_mode,
+)
+from kvax_b200.ops.mask_creator import calculate_mask_sparsity, create_attention_mask, print_mask
 
-__all__ = ["flash_attention", "create_attention_mask", "set_context_parallel_mode", "get_context_parallel_mode"]
+__all__ = ["flash_attention", "create_attention_mask", "calculate_mask_sparsity", "print_mask",
+           "set_context_parallel_mode", "get_context_parallel_mode", "set_backward_mode", "get_backward_mode",
+           "check_last_status", "last_status"]

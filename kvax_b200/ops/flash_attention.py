@@ -34,6 +34,7 @@ import math
 import torch
 
 from kvax_b200 import _lib
+from kvax_b200._status import check_last_status, status_word
 from kvax_b200.utils.common import FlashAttentionParamsConfig, get_default_flash_attention_params
 from kvax_b200.utils.sharding import Mesh, _check_mesh_or_get_global, get_query_context_mesh_axis_name
 from kvax_b200.utils.typing import AttentionMask
@@ -52,6 +53,40 @@ def set_context_parallel_mode(mode: str) -> None:
 
 def get_context_parallel_mode() -> str:
     return _cp_mode
+
+
+_BWD_MODES = ("fused", "two_kernel")
+_bwd_mode = "fused"
+
+
+def set_backward_mode(mode: str) -> None:
+    """Chooses the backward schedule.  "fused" (default): one kv-outer kernel computes dK, dV
+    and dQ with five matrix products per tile pair; dQ is summed with fp32 atomics, so its last
+    bits vary from run to run.  "two_kernel": a dQ kernel and a dK/dV kernel, seven products per
+    tile pair, bit-reproducible.  Head dims the fused kernel does not cover always take the
+    two-kernel path."""
+    global _bwd_mode
+    if mode not in _BWD_MODES:
+        raise ValueError(f"unknown backward mode {mode!r}; expected one of {_BWD_MODES}")
+    _bwd_mode = mode
+
+
+def get_backward_mode() -> str:
+    return _bwd_mode
+
+
+# Workspaces (tile lists, delta, the fp32 dQ accumulator) are scratch that only lives during one call's
+# kernels; calls on one stream run in order, so one buffer per (device, stream, kind) is reused.
+_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def _workspace(kind: str, nbytes: int, device: torch.device) -> torch.Tensor:
+    key = (kind, device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
 
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 192, 256)   # what the reference accepts
@@ -90,26 +125,27 @@ def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, sca
 
 def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: AttentionMask, fwd_blocks, scale,
                       assume_sequential_positions=False, offsets=(0, 0), workspace=None, stages=0, out=None, lse=None):
-    """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2) with lse2 (B, Hq, Sq)
-    fp32, the base-2 log-sum-exp of the scaled scores."""
+    """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2, status) with lse2 (B, Hq, Sq)
+    fp32, the base-2 log-sum-exp of the scaled scores, and the device's status word (a pinned
+    host tensor; see `check_status`).  With `workspace` or `stages` the workspace is returned too."""
     lib = _lib.load()
     B, Sq, Hq, D = q.shape
     out = torch.empty_like(q) if out is None else out
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device) if lse is None else lse
-    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    status, status_ptr = status_word(q.device)
     p = _lib.AttnFwdParams()
     p.stages = int(stages)
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)
-    p.out, p.lse, p.status = out.data_ptr(), lse.data_ptr(), status.data_ptr()
+    p.out, p.lse, p.status = out.data_ptr(), lse.data_ptr(), status_ptr
     ws_bytes = lib.kvax_b200_attn_fwd_workspace_bytes(p)
     if ws_bytes == 0:
         raise _lib.KvaxB200Error("kvax_b200_attn_fwd_workspace_bytes rejected the arguments "
                                  f"(head_dim={D}, dtype={q.dtype})")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if workspace is None else workspace
+    ws = _workspace("fwd", ws_bytes, q.device) if workspace is None else workspace
     with torch.cuda.device(q.device):
-        rc = lib.kvax_b200_attn_fwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
+        rc = lib.kvax_b200_attn_fwd(p, ws.data_ptr(), ws.numel(), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "kvax_b200_attn_fwd")
     if workspace is not None or stages:
         return out, lse, status, ws
@@ -118,34 +154,39 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
 
 def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, mask_dq: AttentionMask,
                        mask_dkdv: AttentionMask, bwd_blocks, scale, assume_sequential_positions=False,
-                       offsets=(0, 0), workspace=None, stages=0, grads=None):
+                       offsets=(0, 0), workspace=None, stages=0, grads=None, mode=None):
     """Direct wrapper of kvax_b200_attn_bwd.  Returns (dq in the input dtype, dk fp32,
-    dv fp32); dk/dv are summed over the query heads of each kv head."""
+    dv fp32, status); dk/dv are summed over the query heads of each kv head.  `mode`:
+    "fused" / "two_kernel" (default: `get_backward_mode()`)."""
     lib = _lib.load()
     if grads is None:
-        dq = torch.empty_like(q)
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)     # dense, whatever the strides of q
         dk = torch.empty(k.shape, dtype=torch.float32, device=k.device)
         dv = torch.empty(v.shape, dtype=torch.float32, device=v.device)
     else:
         dq, dk, dv = grads
-    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    status, status_ptr = status_word(q.device)
     p = _lib.AttnBwdParams()
     p.stages = int(stages)
+    p.flags = _lib.BWD_TWO_KERNEL if (mode or _bwd_mode) == "two_kernel" else 0
     if out.stride() != dout.stride():
         dout = dout.contiguous()
         out = out.contiguous()
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
+    if dq.stride(3) != 1:
+        raise AssertionError("head_dim of dq must be contiguous")
+    p.dq_strides[0], p.dq_strides[1], p.dq_strides[2] = dq.stride(0), dq.stride(1), dq.stride(2)
     p.q, p.k, p.v, p.out, p.dout, p.lse = (t.data_ptr() for t in (q, k, v, out, dout, lse))
     bq, bk = bwd_blocks
     p.mask_dq, keep1 = _block_mask(mask_dq, bk, bq)        # dq mask: block sizes swapped
     p.mask_dkdv, keep2 = _block_mask(mask_dkdv, bq, bk)
-    p.dq, p.dk, p.dv, p.status = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), status.data_ptr()
+    p.dq, p.dk, p.dv, p.status = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), status_ptr
     ws_bytes = lib.kvax_b200_attn_bwd_workspace_bytes(p)
     if ws_bytes == 0:
         raise _lib.KvaxB200Error("kvax_b200_attn_bwd_workspace_bytes rejected the arguments")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if workspace is None else workspace
+    ws = _workspace("bwd", ws_bytes, q.device) if workspace is None else workspace
     with torch.cuda.device(q.device):
-        rc = lib.kvax_b200_attn_bwd(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(q.device).cuda_stream)
+        rc = lib.kvax_b200_attn_bwd(p, ws.data_ptr(), ws.numel(), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(rc, "kvax_b200_attn_bwd")
     if workspace is not None or stages:
         return dq, dk, dv, status, ws
@@ -153,9 +194,11 @@ def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, ma
 
 
 def check_status(status: torch.Tensor, what: str) -> None:
-    """Reads the device status word (synchronises) and raises on a device-side failure."""
+    """Reads a status word and raises on a device-side failure.  The caller synchronises first
+    if the kernels in question may still be running."""
     code = int(status.item())
     if code != 0:
+        status.zero_()
         raise _lib.KvaxB200Error(f"{what}: device status {code} (a bounded wait gave up; 100 + barrier id)")
 
 
@@ -270,11 +313,11 @@ class _FlashAttention(torch.autograd.Function):
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = len(masks)
         ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, offsets, key.dtype)
-        ctx.status = status
         return out
 
     @staticmethod
     def backward(ctx, dout):
+        check_last_status(dout.device)          # a forward that failed on the device: do not differentiate garbage
         saved = ctx.saved_tensors
         query, k_full, v_full, out, lse, q_pos, q_seg, kv_pos, kv_seg = saved[:9]
         flat = saved[9:]
@@ -322,11 +365,11 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = n_masks
         ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype)
-        ctx.status = status
         return _heads_to_seq(out_h, cp, group, permuted)
 
     @staticmethod
     def backward(ctx, dout):
+        check_last_status(dout.device)
         saved = ctx.saved_tensors
         q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg = saved[:9]
         flat = saved[9:]
@@ -369,6 +412,10 @@ def flash_attention(
     """Attention output of shape (batch, query_seq, heads, head_dim), differentiable with
     respect to query, key and value.
 
+    A device-side failure (a bounded wait inside a kernel that gave up) never traps: the kernel
+    finishes and leaves a code in the device's status word, which this function checks on entry,
+    the backward pass checks before it runs, and `kvax_b200.check_last_status()` checks on demand.
+
     `mask` is the tuple returned by `create_attention_mask` (one mask for inference, three
     for training); `fwd_params` / `bwd_params` must be the block sizes those masks were
     built with.  `memory_optimized_gqa_backward` is accepted and has no effect: the dK/dV
@@ -378,6 +425,8 @@ def flash_attention(
     """
     mesh = _check_mesh_or_get_global(mesh)
     axis = get_query_context_mesh_axis_name(mesh)
+    if query.is_cuda:
+        check_last_status(query.device)         # surfaces a failure of an earlier call on this device (no synchronisation)
     if bias is not None:
         raise NotImplementedError("Bias is not supported in Flash multi head attention")
     if query.dim() != 4 or key.dim() != 4 or value.dim() != 4:

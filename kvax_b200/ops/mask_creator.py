@@ -51,20 +51,26 @@ def build_masks(query_positions, query_segment_ids, kv_positions, kv_segment_ids
     p.batch, p.q_len, p.kv_len = B, Sq, Skv
     p.skip_pad_tokens = int(bool(skip_pad_tokens))
     p.n_masks = len(block_specs)
-    outs = []
     for i, (bq, bk, kv_outer) in enumerate(block_specs):
-        n_outer = (Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq
-        arrs = torch.empty((4, B, 1, n_outer), dtype=torch.int32, device=qp.device)
         d = p.masks[i]
         d.q_block, d.kv_block, d.kv_outer = int(bq), int(bk), int(bool(kv_outer))
-        d.lower, d.upper, d.lower_full, d.upper_full = (arrs[j].data_ptr() for j in range(4))
-        outs.append(arrs)
     ws_bytes = lib.kvax_b200_mask_workspace_bytes(p)
     if ws_bytes == 0:
         raise _lib.KvaxB200Error("kvax_b200_mask_workspace_bytes rejected the arguments")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=qp.device)
+    # one allocation holds the workspace and every output array (each output starts on a 256-byte boundary)
+    sizes = [(Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq for (bq, bk, kv_outer) in block_specs]
+    out_bytes = [((4 * B * n * 4 + 255) // 256) * 256 for n in sizes]
+    ws_aligned = ((ws_bytes + 255) // 256) * 256
+    blob = torch.empty(ws_aligned + sum(out_bytes), dtype=torch.uint8, device=qp.device)
+    outs, off = [], ws_aligned
+    for i, n in enumerate(sizes):
+        arrs = blob[off:off + 4 * B * n * 4].view(torch.int32).view(4, B, 1, n)
+        off += out_bytes[i]
+        d = p.masks[i]
+        d.lower, d.upper, d.lower_full, d.upper_full = (arrs[j].data_ptr() for j in range(4))
+        outs.append(arrs)
     with torch.cuda.device(qp.device):
-        rc = lib.kvax_b200_mask_build(p, ws.data_ptr(), ws_bytes, torch.cuda.current_stream(qp.device).cuda_stream)
+        rc = lib.kvax_b200_mask_build(p, blob.data_ptr(), ws_bytes, torch.cuda.current_stream(qp.device).cuda_stream)
     _lib.check(rc, "kvax_b200_mask_build")
     return tuple(AttentionMask(a[0], a[1], a[2], a[3]) for a in outs)
 
@@ -101,35 +107,54 @@ def create_attention_mask(
     return build_masks(query_positions, query_segment_ids, kv_positions, kv_segment_ids, specs, skip_pad_tokens)
 
 
-def calculate_mask_sparsity(mask: AttentionMask, num_inner_blocks: int | None = None) -> float:
-    """Fraction of (outer, inner) block pairs inside [lower, upper): the factor the
-    reference multiplies its dense FLOP formula with (mask_creator.py:601-625)."""
+def calculate_mask_sparsity(mask: AttentionMask, query_block_size: int, kv_block_size: int, query_seq_len: int,
+                            kv_seq_len: int) -> float:
+    """Visited fraction of the block grid: sum over all rows of (upper - lower), divided by
+    (query_seq_len // query_block_size) * (kv_seq_len // kv_block_size) * batch -- the factor the
+    reference multiplies its dense FLOP formula with (mask_creator.py:601-625, same signature and
+    the same floor divisions)."""
     lower = mask.lower_bounds.to(torch.int64)
     upper = mask.upper_bounds.to(torch.int64)
-    if num_inner_blocks is None:
-        num_inner_blocks = int(upper.max().item())
-    total = lower.numel() * max(num_inner_blocks, 1)
-    return float((upper - lower).clamp_min(0).sum().item()) / float(total)
+    batch = lower.shape[0]
+    blocks = float((upper - lower).sum().item())
+    return blocks / (query_seq_len // query_block_size) / (kv_seq_len // kv_block_size) / batch
+
+
+def _mask_grid(mask: AttentionMask, b: int, num_inner_blocks: int):
+    """Class of every (row, inner block) cell of batch entry `b`: 0 not visited, 1 partial, 2 full.
+    A mask with several shards on axis 1 (the dkdv mask under context parallelism) lays the
+    shards side by side, each over num_inner_blocks / shards columns (mask_creator.py:508-537)."""
+    import numpy as np
+    lo, up, lof, upf = (t[b].cpu().numpy() for t in mask.flatten())      # (shards, rows)
+    shards, rows = lo.shape
+    per_shard = num_inner_blocks // shards
+    grid = np.zeros((rows, num_inner_blocks), np.int32)
+    cols = np.arange(per_shard)[None, :]
+    for sh in range(shards):
+        part = np.where((cols >= lof[sh][:, None]) & (cols < upf[sh][:, None]), 2,
+                        np.where((cols >= lo[sh][:, None]) & (cols < up[sh][:, None]), 1, 0))
+        grid[:, sh * per_shard:(sh + 1) * per_shard] = part
+    return grid
 
 
 def print_mask(mask: AttentionMask, num_inner_blocks: int, print_only_first_in_batch: bool = True,
                fit_in_screen: bool = True) -> None:
-    """ASCII picture of a mask: '.' not visited, 'o' partial block, '#' full block."""
-    lo, up, lof, upf = (t.cpu() for t in mask.flatten())
-    batches = 1 if print_only_first_in_batch else lo.shape[0]
+    """Logs a picture of the mask (arguments of mask_creator.py:493-598): two characters per cell,
+    blank = not visited, light shade = partial block, solid = full block.  With `fit_in_screen`
+    a large mask is averaged down to at most 32 rows x 64 columns; an averaged cell is solid
+    only if all its blocks are full and blank only if none is visited."""
+    import numpy as np
+    batches = 1 if print_only_first_in_batch else mask.lower_bounds.shape[0]
+    text = "Attention masks:\n"
     for b in range(batches):
-        n_outer = lo.shape[-1]
-        step_o = max(1, n_outer // 64) if fit_in_screen else 1
-        step_i = max(1, num_inner_blocks // 128) if fit_in_screen else 1
-        lines = []
-        for o in range(0, n_outer, step_o):
-            row = []
-            for i in range(0, num_inner_blocks, step_i):
-                if lof[b, 0, o] <= i < upf[b, 0, o]:
-                    row.append("#")
-                elif lo[b, 0, o] <= i < up[b, 0, o]:
-                    row.append("o")
-                else:
-                    row.append(".")
-            lines.append("".join(row))
-        logger.info("mask for batch %d:\n%s", b, "\n".join(lines))
+        grid = _mask_grid(mask, b, num_inner_blocks).astype(np.float64)
+        rows, cols = grid.shape
+        rs, cs = max(1, -(-rows // 32)), max(1, -(-cols // 64))
+        if fit_in_screen and (rs > 1 or cs > 1):
+            pr, pc = (-rows) % rs, (-cols) % cs
+            g = np.pad(grid, ((0, pr), (0, pc)))
+            grid = g.reshape(g.shape[0] // rs, rs, g.shape[1] // cs, cs).mean(axis=(1, 3))
+        lines = ["".join("\u2588\u2588" if x == 2 else ("  " if x == 0 else "\u2591\u2591") for x in row) for row in grid]
+        rule = "  " + "==" * grid.shape[1] + "  "
+        text += "\n" + rule + "\n" + "".join("||" + ln + "||\n" for ln in lines) + rule + "\n\n"
+    logger.info(text)

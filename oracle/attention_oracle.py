@@ -117,3 +117,82 @@ def attention_fwd_bwd_torch(q, k, v, q_pos, q_seg, kv_pos, kv_seg, scale, dout, 
     out = torch.einsum("bhqk,bkhd->bqhd", p, vv)
     (out * dout).sum().backward()
     return out.detach(), q.grad, k.grad, v.grad
+
+
+def attention_dense_torch(q, k, v, q_pos, q_seg, kv_pos, kv_seg, scale, dout=None, kv_heads=None, batch_rows=None,
+                          q_chunk=4096):
+    """The same dense masked attention and its analytic gradients with torch fp32 ops, on whatever
+    device the inputs live on, evaluated in blocks of `q_chunk` query rows against the key range
+    their segment ids can match, so that sequences of 10^4 - 10^5 tokens fit in memory.  It is the
+    fp32 reference of the parity tests at the benchmark sizes, where the NumPy loops above would
+    take hours; tests/test_oracle_attention.py checks it against those loops on small cases.
+
+    q (B, Sq, Hq, D), k / v (B, Skv, Hkv, D) tensors of any float dtype (computed in fp32; fp32
+    matmuls must not be allowed to use tf32).  `kv_heads` / `batch_rows`: subsets to evaluate
+    (default all); a kv head is always evaluated with all query heads of its group, because
+    dk / dv sum over the group.  Returns a dict: out (B, Sq, Hq, Dv), lse2 (B, Hq, Sq) and, with
+    `dout`, dq, dk, dv -- zeros outside the evaluated subsets -- plus the lists of evaluated
+    batch rows, kv heads and query heads.  Key ranges are found from segment ids, which must be
+    piecewise constant along the sequence (documents are contiguous), as everywhere in this repo.
+    """
+    import math
+
+    import torch
+
+    assert not torch.backends.cuda.matmul.allow_tf32
+    dev = q.device
+    B, Sq, Hq, D = q.shape
+    Skv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    G = Hq // Hkv
+    kv_heads = list(range(Hkv)) if kv_heads is None else list(kv_heads)
+    batch_rows = list(range(B)) if batch_rows is None else list(batch_rows)
+    q_pos, q_seg, kv_pos, kv_seg = (torch.as_tensor(t).to(dev) for t in (q_pos, q_seg, kv_pos, kv_seg))
+    out = torch.zeros((B, Sq, Hq, Dv), dtype=torch.float32, device=dev)
+    lse2 = torch.zeros((B, Hq, Sq), dtype=torch.float32, device=dev)
+    grads = dout is not None
+    if grads:
+        dq = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=dev)
+        dk = torch.zeros((B, Skv, Hkv, D), dtype=torch.float32, device=dev)
+        dv = torch.zeros((B, Skv, Hkv, Dv), dtype=torch.float32, device=dev)
+    for b in batch_rows:
+        for s in range(0, Sq, q_chunk):
+            e = min(Sq, s + q_chunk)
+            qs_, qp_ = q_seg[b, s:e], q_pos[b, s:e]
+            # keys whose segment id occurs among this block's queries form one index range
+            lo_id, hi_id = int(qs_.min()), int(qs_.max())
+            cand = torch.nonzero((kv_seg[b] >= lo_id) & (kv_seg[b] <= hi_id))
+            if cand.numel() == 0:
+                continue
+            k0, k1 = int(cand.min()), int(cand.max()) + 1
+            mask = (qs_[:, None] == kv_seg[b, k0:k1][None, :]) & (qp_[:, None] >= kv_pos[b, k0:k1][None, :])
+            for g in kv_heads:
+                hs = slice(g * G, (g + 1) * G)
+                qg = q[b, s:e, hs].float().permute(1, 0, 2)                     # (G, qc, D)
+                kg, vg = k[b, k0:k1, g].float(), v[b, k0:k1, g].float()         # (kc, D)
+                sc = torch.matmul(qg, kg.t()) * scale                           # (G, qc, kc)
+                sc = sc.masked_fill(~mask[None], float("-inf"))
+                m = sc.amax(-1, keepdim=True)
+                m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+                p = torch.exp(sc - m)
+                del sc
+                l = p.sum(-1, keepdim=True)
+                p = p / torch.where(l > 0, l, torch.ones_like(l))
+                out[b, s:e, hs] = torch.matmul(p, vg).permute(1, 0, 2)
+                l2 = (m + torch.log(torch.where(l > 0, l, torch.ones_like(l)))) / math.log(2.0)
+                lse2[b, hs, s:e] = torch.where(l > 0, l2, torch.full_like(l2, float("inf")))[:, :, 0]
+                if grads:
+                    dog = dout[b, s:e, hs].float().permute(1, 0, 2)             # (G, qc, Dv)
+                    dv[b, k0:k1, g] += torch.matmul(p.transpose(1, 2), dog).sum(0)
+                    dp = torch.matmul(dog, vg.t())
+                    delta = (p * dp).sum(-1, keepdim=True)
+                    ds = p * (dp - delta) * scale
+                    del dp
+                    dq[b, s:e, hs] = torch.matmul(ds, kg).permute(1, 0, 2)
+                    dk[b, k0:k1, g] += torch.matmul(ds.transpose(1, 2), qg).sum(0)
+                    del ds
+                del p
+    res = dict(out=out, lse2=lse2, batch_rows=batch_rows, kv_heads=kv_heads,
+               q_heads=[h for g in kv_heads for h in range(g * G, (g + 1) * G)])
+    if grads:
+        res.update(dq=dq, dk=dk, dv=dv)
+    return res

@@ -76,7 +76,10 @@ def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=Tr
             # out and dq come from identical kernels on identical data: exact.  With the
             # all-gather schedule dk/dv are summed over ranks in fp32 in a different order before
             # the bf16 cast; with the head exchange they too are the single-GPU values.
-            if name in ("out", "dq") or mode == "head_exchange":
+            exact = name in ("out", "dq") or mode == "head_exchange"
+            if kv.get_backward_mode() == "fused" and name == "dq":
+                exact = False        # the fused backward sums dQ tiles with fp32 atomics: equal to rounding, not bit for bit
+            if exact:
                 assert err == 0.0, f"{name}: CP differs from single GPU (max {err})"
             else:
                 assert rel < 4e-3 and err <= 2e-2 + r.abs().max().item() / 128, f"{name}: {err} {rel}"
@@ -144,6 +147,11 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
     res = {}
+    # the default (fused) backward first, then everything on the bit-reproducible two-kernel backward
+    res["fused_docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=4, hkv=2, pad=0.05, sequential=False)
+    res["fused_hx_docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=world, pad=0.05,
+                                       sequential=False, mode="head_exchange")
+    kv.set_backward_mode("two_kernel")
     res["docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=4, hkv=2, pad=0.05, sequential=False)
     res["batch2_seqpos"] = run_case(rank, world, dev, seq=512 * world, batch=2, hq=2, hkv=2, pad=0.0, sequential=True)
     res["no_permute"] = run_case(rank, world, dev, seq=512 * world, batch=1, hq=2, hkv=1, pad=0.1, sequential=False, permuted=False)
@@ -153,6 +161,7 @@ def main():
     res["hx_no_permute"] = run_case(rank, world, dev, seq=512 * world, batch=1, hq=world, hkv=world, pad=0.1, sequential=False, permuted=False, mode=hx)
     kv.set_context_parallel_mode("auto")
     res["tensor_parallel"] = run_tp_case(rank, world, dev)
+    kv.set_backward_mode("fused")
     dist.barrier()
     if rank == 0:
         print("cp gpu worker ok", {k: ({n: (round(e, 5), round(r, 5)) for n, (e, r) in v.items()} if isinstance(v, dict) else v) for k, v in res.items()})

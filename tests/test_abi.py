@@ -26,6 +26,14 @@ def test_every_declared_symbol_is_exported(lib):
         assert hasattr(lib, name), name
 
 
+def test_header_is_plain_c():
+    """The boundary is a C ABI: the header has to compile as C99 on its own."""
+    import subprocess
+    res = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c",
+                          os.path.join(ROOT, "include", "kvax_b200.h")], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+
+
 def test_version_and_error_strings(lib):
     assert b"sm_100a" in lib.kvax_b200_version()
     assert lib.kvax_b200_error_string(0) == b"ok"
@@ -51,3 +59,17 @@ def test_struct_sizes_match_the_header():
     assert ctypes.sizeof(_lib.MaskDesc) == 48
     assert ctypes.sizeof(_lib.BlockMask) == 40
     assert ctypes.sizeof(_lib.AttnShape) == 4 * 10 + 8 * 12 + 8 * 4 + 8
+    # checked against the C compiler: sizeof of every struct of the header
+    import subprocess
+    import tempfile
+    src = '#include <stdio.h>\n#include "kvax_b200.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu\\n",' \
+          "sizeof(kvax_b200_mask_desc),sizeof(kvax_b200_mask_params),sizeof(kvax_b200_block_mask),sizeof(kvax_b200_attn_shape)," \
+          "sizeof(kvax_b200_attn_fwd_params),sizeof(kvax_b200_attn_bwd_params));return 0;}\n"
+    with tempfile.TemporaryDirectory() as d:
+        with open(os.path.join(d, "s.c"), "w") as f:
+            f.write(src)
+        subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), os.path.join(d, "s.c"), "-o", os.path.join(d, "s")],
+                       check=True)
+        sizes = [int(x) for x in subprocess.run([os.path.join(d, "s")], capture_output=True, text=True, check=True).stdout.split()]
+    mirrors = (_lib.MaskDesc, _lib.MaskParams, _lib.BlockMask, _lib.AttnShape, _lib.AttnFwdParams, _lib.AttnBwdParams)
+    assert sizes == [ctypes.sizeof(m) for m in mirrors]

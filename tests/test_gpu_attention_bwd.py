@@ -12,7 +12,7 @@ from oracle import generators as gen
 pytestmark = pytest.mark.gpu
 
 
-def _run_fwd_bwd(inp, fwd_blocks=(128, 128), bwd_blocks=(128, 128), sequential=False):
+def _run_fwd_bwd(inp, fwd_blocks=(128, 128), bwd_blocks=(128, 128), sequential=False, mode=None):
     from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status
     from kvax_b200.ops.mask_creator import build_masks
 
@@ -22,7 +22,7 @@ def _run_fwd_bwd(inp, fwd_blocks=(128, 128), bwd_blocks=(128, 128), sequential=F
     masks = build_masks(p, s, p, s, [(fwd_blocks[0], fwd_blocks[1], False), (bk, bq, False), (bq, bk, True)], True)
     out, lse, st = attention_forward(q, k, v, p, s, p, s, masks[0], fwd_blocks, inp["scale"], sequential)
     dq, dk, dv, st2 = attention_backward(q, k, v, out, do, lse, p, s, p, s, masks[1], masks[2], bwd_blocks,
-                                         inp["scale"], sequential)
+                                         inp["scale"], sequential, mode=mode)
     torch.cuda.synchronize()
     check_status(st, "attn_fwd")
     check_status(st2, "attn_bwd")
@@ -49,12 +49,37 @@ def _check(inp, dq, dk, dv):
     compare("dv", dv, rv, rows)
 
 
+@pytest.mark.parametrize("mode", ["fused", "two_kernel"])
 @pytest.mark.parametrize("head_dim", [128, 64])
 @pytest.mark.parametrize("hq,hkv", [(4, 2), (4, 4), (4, 1)])
-def test_backward_small_docmask(head_dim, hq, hkv):
+def test_backward_small_docmask(head_dim, hq, hkv, mode):
+    """Both backward schedules (head_dim 64 always takes the two-kernel path)."""
     cfg = gen.small_config(seq=1024, hq=hq, hkv=hkv, head_dim=head_dim)
     inp = _zero_pad_dout(gen.make_inputs(cfg, seed=3))
-    _, dq, dk, dv = _run_fwd_bwd(inp)
+    _, dq, dk, dv = _run_fwd_bwd(inp, mode=mode)
+    _check(inp, dq, dk, dv)
+
+
+def test_fused_backward_agrees_with_two_kernel_backward():
+    """Same P and dS in both schedules, accumulated in the same order for dK / dV: those are
+    bit-identical.  dQ is summed tile by tile with fp32 atomics in the fused schedule and in
+    TMEM in the other: equal to rounding."""
+    cfg = gen.small_config(seq=4096, batch=2, hq=8, hkv=2, head_dim=128, doc_min=100, doc_max=3000, pad=0.06)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=41))
+    _, dq_f, dk_f, dv_f = _run_fwd_bwd(inp, mode="fused")
+    _, dq_t, dk_t, dv_t = _run_fwd_bwd(inp, mode="two_kernel")
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    np.testing.assert_array_equal(np.where(rows, dk_f, 0), np.where(rows, dk_t, 0))
+    np.testing.assert_array_equal(np.where(rows, dv_f, 0), np.where(rows, dv_t, 0))
+    compare("dq fused vs two-kernel", dq_f, dq_t, rows, max_abs=1e-2 + np.abs(dq_t).max() / 128, rel_l2=4e-3)
+
+
+@pytest.mark.parametrize("sequential", [False, True])
+def test_fused_backward_sequential_and_global_positions(sequential):
+    """assume_sequential_positions on the fused path (the causal test compares indices)."""
+    cfg = gen.small_config(seq=2048, batch=1, hq=4, hkv=2, head_dim=128, doc_min=100, doc_max=900, pad=0.05)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=43, restart_positions=False))
+    _, dq, dk, dv = _run_fwd_bwd(inp, sequential=sequential, mode="fused")
     _check(inp, dq, dk, dv)
 
 
@@ -84,12 +109,57 @@ def test_backward_tiny_config_c1():
 
 
 def test_backward_deterministic():
+    """The two-kernel backward is bit-reproducible; the fused one is for dK and dV (dQ is summed
+    with fp32 atomics)."""
     cfg = gen.small_config(seq=2048, hq=4, hkv=1, head_dim=128)
     inp = _zero_pad_dout(gen.make_inputs(cfg, seed=13))
-    a = _run_fwd_bwd(inp)
-    b = _run_fwd_bwd(inp)
+    a = _run_fwd_bwd(inp, mode="two_kernel")
+    b = _run_fwd_bwd(inp, mode="two_kernel")
     for x, y in zip(a, b):
         np.testing.assert_array_equal(x, y)
+    c = _run_fwd_bwd(inp, mode="fused")
+    d = _run_fwd_bwd(inp, mode="fused")
+    for i in (0, 2, 3):
+        np.testing.assert_array_equal(c[i], d[i])
+
+
+@pytest.mark.parametrize("bwd_blocks", [(64, 128), (128, 64)])
+def test_backward_mask_block_sizes_fused(bwd_blocks):
+    cfg = gen.small_config(seq=1024, hq=2, hkv=1, head_dim=128, doc_min=40, doc_max=500)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=5, restart_positions=True))
+    _, dq, dk, dv = _run_fwd_bwd(inp, bwd_blocks=bwd_blocks, mode="fused")
+    _check(inp, dq, dk, dv)
+
+
+def test_strided_qkv_from_one_fused_projection():
+    """q, k, v sliced out of one (B, S, Hq + 2 Hkv, D) tensor, as a fused QKV projection hands them
+    over: the kernels read them through strided tensor maps and dq comes back dense."""
+    import kvax_b200 as kv
+    cfg = gen.small_config(seq=1024, batch=2, hq=4, hkv=2, head_dim=128)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=47))
+    fused = torch.cat([to_bf16_cuda(inp[n]) for n in ("q", "k", "v")], dim=2).contiguous().requires_grad_(True)
+    q, k, v = fused[:, :, :4], fused[:, :, 4:6], fused[:, :, 6:8]
+    assert not q.is_contiguous()
+    do = to_bf16_cuda(inp["dout"])
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    mesh = kv.Mesh(("data", "context"), (1, 1), rank=0)
+    rq, rk, rv = _oracle_grads(inp)
+    rows = (inp["segment_ids"] != -1)[:, :, None, None]
+    for mode in ("fused", "two_kernel"):
+        kv.set_backward_mode(mode)
+        try:
+            fused.grad = None
+            with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+                masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+                out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+                out.backward(do)
+        finally:
+            kv.set_backward_mode("fused")
+        g = fused.grad.float().cpu().numpy()
+        compare(f"dq[{mode}]", g[:, :, :4], rq, rows, bf16_output=True)
+        compare(f"dk[{mode}]", g[:, :, 4:6], rk, rows, max_abs=2e-2 + np.abs(rk).max() / 128)
+        compare(f"dv[{mode}]", g[:, :, 6:8], rv, rows, max_abs=2e-2 + np.abs(rv).max() / 128)
 
 
 def test_backward_linearity_in_dout():

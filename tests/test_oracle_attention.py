@@ -43,3 +43,33 @@ def test_oracle_matches_reference_attention(path):
         for name, got, ref, m in (("dq", dq, z["dq"], sel), ("dk", dk, z["dk"], krows), ("dv", dv, z["dv"], krows)):
             err = np.abs(np.where(m, got - ref, 0)).max()
             assert err <= 2e-5 * max(1.0, np.abs(ref).max()), f"{name}: {err}"
+
+
+@pytest.mark.parametrize("q_chunk", [64, 4096])
+def test_blocked_torch_reference_matches_the_dense_oracle(q_chunk):
+    """`attention_dense_torch` (the fp32 reference of the parity tests at benchmark sizes) against
+    the NumPy oracle above, on a document-masked GQA case with PAD, whole and in small blocks."""
+    import torch
+    from oracle import generators as gen
+
+    cfg = gen.small_config(seq=512, batch=2, hq=4, hkv=2, head_dim=64, doc_min=40, doc_max=300, pad=0.08)
+    inp = gen.make_inputs(cfg, seed=3)
+    p, s = inp["positions"], inp["segment_ids"]
+    do = np.where((s != -1)[:, :, None, None], inp["dout"], 0.0).astype(np.float32)
+    out, lse2 = ao.attention_forward(inp["q"], inp["k"], inp["v"], p, s, p, s, inp["scale"])
+    dq, dk, dv = ao.attention_backward(inp["q"], inp["k"], inp["v"], p, s, p, s, inp["scale"], do)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    res = ao.attention_dense_torch(t(inp["q"]), t(inp["k"]), t(inp["v"]), p, s, p, s, inp["scale"], t(do), q_chunk=q_chunk)
+    rows = (s != -1)
+    sel = rows[:, :, None, None]
+    for name, got, ref in (("out", res["out"], out), ("dq", res["dq"], dq), ("dk", res["dk"], dk), ("dv", res["dv"], dv)):
+        err = np.abs(np.where(sel, got.numpy() - ref, 0)).max()
+        assert err <= 3e-5 * max(1.0, np.abs(ref).max()), f"{name}: {err}"
+    err = np.abs(np.where(rows[:, None, :], res["lse2"].numpy() - lse2, 0)).max()
+    assert err <= 3e-5
+    # a subset of kv heads / batch rows leaves the rest zero and equals the full result where evaluated
+    sub = ao.attention_dense_torch(t(inp["q"]), t(inp["k"]), t(inp["v"]), p, s, p, s, inp["scale"], t(do), kv_heads=[1],
+                                   batch_rows=[1], q_chunk=q_chunk)
+    assert sub["q_heads"] == [2, 3]
+    np.testing.assert_array_equal(sub["dq"][1, :, 2:4].numpy(), res["dq"][1, :, 2:4].numpy())
+    assert float(sub["dq"][0].abs().max()) == 0.0 and float(sub["dk"][1, :, 0].abs().max()) == 0.0
