@@ -45,6 +45,24 @@
 
 namespace kvx {
 
+// Optional phase clocks (compiled in with -DKVAX_PHASE_CLOCKS only): lane 0 of one warp per role sums
+// the clock64 cycles it spends in each phase of its loop and stores the sums per CTA, so that a run
+// shows which waits and which work make up an item.  Off in the shipped library.
+#ifdef KVAX_PHASE_CLOCKS
+__device__ unsigned int* g_phase_clocks = nullptr;       // (grid, 4 roles, 12 slots)
+#define PH_BEGIN() unsigned int ph_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long ph_t = clock64();
+#define PH(slot) { const long long ph_now = clock64(); ph_acc[slot] += (unsigned int)(ph_now - ph_t); ph_t = ph_now; }
+#define PH_END(role, items) \
+  if (g_phase_clocks && lane == 0) { \
+    ph_acc[11] = (unsigned int)(items); \
+    for (int s_ = 0; s_ < 12; ++s_) g_phase_clocks[((long long)blockIdx.x * 4 + (role)) * 12 + s_] = ph_acc[s_]; \
+  }
+#else
+#define PH_BEGIN()
+#define PH(slot)
+#define PH_END(role, items)
+#endif
+
 namespace {
 
 constexpr int kTmemCols = 512;
@@ -155,16 +173,19 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     bool ok = true;
     uint32_t e_next = __ldg(list);                 // list entries are fetched one iteration ahead
     int li = 0, qh = kvh * group;                  // index into the list, query head
+    PH_BEGIN()
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const int u = int(e_next & ~kPartialBit);
       const int yh = qh;
       if (++li == cnt) { li = 0; ++qh; }
       if (i + 1 < n) e_next = __ldg(list + li);
+      PH(1)
       if (i >= 2) {
         ok = mbar_wait(&bars[F_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, F_YEMPTY0 + st);
         ok = __all_sync(0xffffffffu, ok);
       }
+      PH(0)
       if (!ok) break;
       uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
       uint8_t* y2 = y1 + L::kTileBytes;
@@ -199,6 +220,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       }
       __syncwarp();
     }
+    PH_END(3, n)
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
     constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);    // X (K-major) x Y (K-major)
@@ -235,6 +257,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       }
       __syncwarp();
     }
+    PH_BEGIN()
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const uint32_t ph = uint32_t(i & 1);
@@ -243,6 +266,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       const uint32_t acc_on = (i > 0) ? 1u : 0u;
       const bool more = (i + 1 < n);
       wait(F_PFULL, ph, true);                                                      // P^T(i) written, S^T(i) consumed
+      PH(0)
       if (!ok) break;
       if (elect_one()) {
         // dV += P^T dO: the half h of the register-math threads wrote its four K-steps at column offset 64 h
@@ -253,16 +277,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         umma_commit(&bars[F_DVDONE]);                                               // the dO slot may now take dS^T
       }
       __syncwarp();
+      PH(1)
       if (more) {
         wait(F_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
+        PH(2)
         if (!ok) break;
         if (elect_one()) {
           issue_t(tT1, x1_lo, sdesc_lo_sw128(y1n, 16));                             // scores of item i+1
           umma_commit(&bars[F_SFULL]);
         }
         __syncwarp();
+        PH(3)
       }
       wait(F_DSFULL, ph, true);                                                     // dS^T(i) in the dO slot, dP^T(i) consumed
+      PH(4)
       if (!ok) break;
       if (elect_one()) {
         // dQ(i) = dS K over the dP^T columns: both operands read with kv as the contraction index (16 kv rows per
@@ -284,16 +312,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         if (!more) umma_commit(&bars[F_ACCFULL]);
       }
       __syncwarp();
+      PH(5)
       if (more) {
         wait(F_DRAINED, ph, true);                                                  // dQ(i) has left the T2 columns
+        PH(6)
         if (!ok) break;
         if (elect_one()) {
           issue_t(tT2, x2_lo, sdesc_lo_sw128(y2n, 16));                             // dP^T of item i+1
           umma_commit(&bars[F_DPFULL]);
         }
         __syncwarp();
+        PH(7)
       }
     }
+    PH_END(1, n)
   } else if (is_compute) {
     // ------------------------------------------------------------------ register math
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
@@ -336,6 +368,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     bool ok = true;
     uint32_t e_next = __ldg(list);
     int li = 0;
+    PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
       const uint32_t e = e_next;
       if (++li == count) li = 0;
@@ -351,12 +384,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (partial) { keep[0] = chunk_keep(c0 + cb); keep[1] = chunk_keep(c0 + cb + 32); }
 
+      PH(0)
       // LSE2 / delta of this item have landed together with its Q and dO tiles
       ok = mbar_wait(&bars[F_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, F_YFULL0 + st);
+      PH(1)
       if (!ok) break;
 
       // ---- A: P^T = exp2(S^T * scale*log2e - LSE2); the 64 values of this thread stay in registers for B
       ok = mbar_wait(&bars[F_SFULL], ph, abort_flag, a.status, F_SFULL);
+      PH(2)
       if (!ok) break;
       tc_fence_after();
       uint32_t v[2][32];
@@ -384,14 +420,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[F_PFULL]);
+      PH(3)
 
       // ---- B: dS^T = P^T * (dP^T - delta) -> bf16 -> the shared-memory slot of dO(i), dead once dV(i) has run
       ok = mbar_wait(&bars[F_DPFULL], ph, abort_flag, a.status, F_DPFULL);
+      PH(4)
       if (!ok) break;
       tc_fence_after();
       uint32_t dp[2][16];                                     // 16 columns at a time, the next request in flight
       tmem_ld16(my_t2, dp[0]);
       ok = mbar_wait(&bars[F_DVDONE], ph, abort_flag, a.status, F_DVDONE);
+      PH(5)
       if (!ok) break;
       {
         // kv row `row`, queries [64 half, 64 half + 64) = one 128-byte row of box `half`: eight 16-byte chunks at the
@@ -419,7 +458,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars[F_DSFULL]);
+      PH(6)
     }
+    if (warp == 0) { PH_END(0, n_items) }
 
     if (ok) ok = mbar_wait(&bars[F_ACCFULL], 0, abort_flag, a.status, F_ACCFULL);
     if (ok) {
@@ -453,12 +494,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     bool ok = true;
     uint32_t e_next = __ldg(list);
     int li = 0, qh = kvh * group;
+    PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
       const int q0 = int(e_next & ~kPartialBit) * kTile + dw * 32;    // first query row this warp drains
       const int yh = qh;
       if (++li == count) { li = 0; ++qh; }
       if (i + 1 < n_items) e_next = __ldg(list + li);
       ok = mbar_wait(&bars[F_DQFULL], uint32_t(i & 1), abort_flag, a.status, F_DQFULL);
+      PH(0)
       if (!ok) break;
       tc_fence_after();
       // Registers hold three 32-column chunks at a time (the register file leaves 128 per thread): chunks 0-2 are
@@ -495,9 +538,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         tmem_ld_wait(x0);
         tc_fence_before();
         mbar_arrive(&bars[F_DRAINED]);                        // the T2 columns may take dP^T(i+1)
+        PH(1)
         stage_out(1, x1);
         stage_out(2, x2);
         stage_out(3, x0);
+        PH(2)
       } else {
         uint32_t x0[32], x1[32];
         tmem_ld32(tT2 + lane_base, x0);
@@ -510,6 +555,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         stage_out(1, x1);
       }
     }
+    if (dw == 0) { PH_END(2, n_items) }
     if (lane == 0) bulk_wait_group<0>();                      // all reduce-adds performed before the CTA goes away
     __syncwarp();
   }
@@ -562,6 +608,13 @@ int launch_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
 }  // namespace
 
 bool attn_bwd_fused_supports(int head_dim) { return head_dim == 128; }
+
+#ifdef KVAX_PHASE_CLOCKS
+// profiling builds only: where the phase clocks go ((grid, 4, 12) uint32 in device memory), or null
+extern "C" int kvax_b200_debug_set_phase_buffer(unsigned int* buf) {
+  return cudaMemcpyToSymbol(g_phase_clocks, &buf, sizeof(buf)) == cudaSuccess ? 0 : -4;
+}
+#endif
 
 int launch_attn_bwd_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
   if (L.head_dim == 128) return launch_fused<128>(L, stream);
