@@ -2,23 +2,24 @@
 // five matrix products per tile pair (S, dP, dV, dK, dQ) and one exponential per score, instead
 // of the seven products and two exponentials of the dQ kernel + dK/dV kernel pair in attn_bwd.cu.
 //
-// CTA = (128-row kv tile, kv head, batch); K and V of the tile stay in shared memory; the Q and dO
-// tiles of every query head of the GQA group x every listed query tile stream through a two-stage
-// TMA ring.  Fourteen warps:
+// CTA = (128-row kv tile, kv head, batch); K and V of the tile stay in shared memory; the Q tiles
+// (with the 128 LSE2 / delta values of their queries) of every query head of the GQA group x every
+// listed query tile stream through a two-stage TMA ring, the dO tiles through a single buffer (dO is
+// dead once dV has run, long before the next dP needs its successor).  Fourteen warps:
 //   warps 0-7   register math.  Thread t owns kv row t % 128 (= TMEM lane) and the 64-column half
 //               t / 128 of every 128 x 128 tile:
 //                 A: P^T = exp2(S^T * scale*log2e - LSE2), masked, -> bf16 -> TMEM (over S^T)
-//                 B: dS^T = P^T * (dP^T - delta) -> bf16 -> shared memory, into the slot of dO(i),
-//                    which is dead once dV(i) has run; written in the 128-byte-swizzled layout TMA
-//                    produces, so the one copy serves as K-major A operand of dK and as MN-major A
-//                    operand of dQ.
-//   warps 8-11  dQ drain.  Warp w owns TMEM lanes 32 (w % 4) ...: it pulls the finished 128 x D fp32
-//               dQ tile out of TMEM (freeing the columns for the next dP at once), stages it through a
-//               private double-buffered 4 KB area and adds it to the fp32 dQ accumulator in global
-//               memory with TMA tile reduce-adds (cp.reduce.async.bulk.tensor, this GPU's own memory,
-//               no multicast) -- asynchronously, while the register-math warps work on the next item.
-//   warp 12     TMA producer (K, V once; per item Q, dO and the 128 LSE2 / delta values of the query
-//               tile) and TMEM allocation.
+//                 B: dS^T = P^T * (dP^T - delta) -> bf16 -> a shared-memory tile of its own, written
+//                    in the 128-byte-swizzled layout TMA produces, so the one copy serves as the
+//                    K-major A operand of dK and as the MN-major A operand of dQ.
+//   warps 8-11  dQ drain.  Warp w owns TMEM lanes 32 (w % 4) ... = 32 query rows of the finished
+//               128 x D fp32 dQ tile.  It pulls them into registers (which frees the TMEM columns for
+//               the next dP^T), stages them through a private double-buffered 4 KB area and adds them
+//               to the fp32 dQ accumulator in global memory with TMA tile reduce-adds
+//               (cp.reduce.async.bulk.tensor, this GPU's own memory, no multicast) -- asynchronously,
+//               beside the register math of the next item.  (Plain red.global.add from registers was
+//               measured three times slower: the SM issues one 128-byte reduction every ~20 cycles.)
+//   warp 12     TMA producer and TMEM allocation.
 //   warp 13     MMA issuer (whole warp runs the loop, one elected lane issues):
 //                 S^T(0) dP^T(0) | dV(i) S^T(i+1) | dQ(i) dK(i) | dP^T(i+1) | ...
 //               S^T  = K Q^T        (SS)            -> T1
@@ -29,7 +30,8 @@
 // TMEM (512 columns): T1 | T2 | dV | dK.  dQ shares its columns with dP^T: that makes
 // dP^T(i) -> dS^T(i) -> dQ(i) -> drain -> dP^T(i+1) one serial chain, which the other chain
 // S^T(i+1) -> P^T(i+1) -> dV(i+1) overlaps.
-// Shared memory (D = 128): K, V 64 KB + 2 x (Q, dO) 128 KB + drain staging 32 KB + LSE2/delta 2 KB.
+// Shared memory (D = 128): K, V 64 KB + 2 x Q 64 KB + dO 32 KB + dS^T 32 KB + drain staging 32 KB +
+// LSE2 / delta 2 KB.
 //
 // dQ is accumulated with fp32 atomics at L2, so its summation order (and last bits) vary from run
 // to run; dK and dV are accumulated in TMEM in a fixed order.
@@ -75,17 +77,19 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;          // 448
 constexpr int kSlice = kTile / 2;                      // columns per register-math thread
 constexpr int kStageBuf = 32 * 32 * 4;                 // one drain staging buffer: 32 rows x 32 fp32
 
-enum FBar { F_XFULL = 0, F_YFULL0, F_YFULL1, F_YEMPTY0, F_YEMPTY1, F_SFULL, F_PFULL, F_DPFULL, F_DVDONE, F_DSFULL,
-            F_DQFULL, F_DRAINED, F_ACCFULL, F_COUNT };
+enum FBar { F_XFULL = 0, F_QFULL0, F_QFULL1, F_QEMPTY0, F_QEMPTY1, F_DOFULL, F_DOEMPTY, F_SFULL, F_PFULL, F_DPFULL,
+            F_DSFULL, F_DQFULL, F_DRAINED, F_ACCFULL, F_COUNT };
 
 template <int D>
 struct FusedSmem {
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kBoxBytes = kTile * 64 * 2;
   static constexpr int kX1 = 0, kX2 = kTileBytes;
-  static constexpr int kY = 2 * kTileBytes;                       // stage s: Q at kY + s*2*tile, dO (later dS^T) right after
-  static constexpr int kStage = 6 * kTileBytes;                   // drain warp w, buffer u: kStage + (2 w + u) * kStageBuf
-  static constexpr int kCols = kStage + kDrainWarps * 2 * kStageBuf;   // stage s: lse2[128] | delta[128]
+  static constexpr int kQ = 2 * kTileBytes;                       // Q stage s at kQ + s * tile
+  static constexpr int kDO = 4 * kTileBytes;                      // dO, single buffer
+  static constexpr int kDS = 5 * kTileBytes;                      // dS^T tile: 128 kv rows x 128 queries bf16 (two boxes)
+  static constexpr int kStage = kDS + kTile * kTile * 2;          // drain warp w, buffer u: kStage + (2 w + u) * kStageBuf
+  static constexpr int kCols = kStage + kDrainWarps * 2 * kStageBuf;   // Q stage s: lse2[128] | delta[128]
   static constexpr int kColBytes = kTile * 4;
   static constexpr int kBars = kCols + 2 * 2 * kColBytes;
   static constexpr int kTmemSlot = kBars + 8 * F_COUNT;
@@ -181,14 +185,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       if (++li == cnt) { li = 0; ++qh; }
       if (i + 1 < n) e_next = __ldg(list + li);
       PH(1)
+      // ---- Q(i) with LSE2 / delta: its stage is free once dK(i-2) has completed
       if (i >= 2) {
-        ok = mbar_wait(&bars[F_YEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, F_YEMPTY0 + st);
+        ok = mbar_wait(&bars[F_QEMPTY0 + st], ((i >> 1) - 1) & 1, abort_flag, a.status, F_QEMPTY0 + st);
         ok = __all_sync(0xffffffffu, ok);
       }
       PH(0)
       if (!ok) break;
-      uint8_t* y1 = smem + L::kY + st * 2 * L::kTileBytes;
-      uint8_t* y2 = y1 + L::kTileBytes;
+      uint8_t* yq = smem + L::kQ + st * L::kTileBytes;
       float* cs = s_cols + st * 2 * kTile;
       const int col0 = u * kTile;
       const float* lse_src = a.lse + ((long long)b * a.q_heads + yh) * q_len + col0;
@@ -207,16 +211,27 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       }
       __syncwarp();
       if (elect_one()) {
-        mbar_arrive_expect_tx(&bars[F_YFULL0 + st], 2 * L::kTileBytes + (bulk ? 2 * L::kColBytes : 0));
+        mbar_arrive_expect_tx(&bars[F_QFULL0 + st], L::kTileBytes + (bulk ? 2 * L::kColBytes : 0));
 #pragma unroll
-        for (int x = 0; x < D / 64; ++x) {
-          tma_load_4d(y1 + x * L::kBoxBytes, &tmap_q, &bars[F_YFULL0 + st], x * 64, yh, u * kTile, b);
-          tma_load_4d(y2 + x * L::kBoxBytes, &tmap_do, &bars[F_YFULL0 + st], x * 64, yh, u * kTile, b);
-        }
+        for (int x = 0; x < D / 64; ++x) tma_load_4d(yq + x * L::kBoxBytes, &tmap_q, &bars[F_QFULL0 + st], x * 64, yh, u * kTile, b);
         if (bulk) {
-          bulk_load_1d(cs, lse_src, L::kColBytes, &bars[F_YFULL0 + st]);
-          bulk_load_1d(cs + kTile, dl_src, L::kColBytes, &bars[F_YFULL0 + st]);
+          bulk_load_1d(cs, lse_src, L::kColBytes, &bars[F_QFULL0 + st]);
+          bulk_load_1d(cs + kTile, dl_src, L::kColBytes, &bars[F_QFULL0 + st]);
         }
+      }
+      __syncwarp();
+      // ---- dO(i): the single buffer is free once dV(i-1) has completed
+      if (i >= 1) {
+        ok = mbar_wait(&bars[F_DOEMPTY], uint32_t((i - 1) & 1), abort_flag, a.status, F_DOEMPTY);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      PH(2)
+      if (!ok) break;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&bars[F_DOFULL], L::kTileBytes);
+#pragma unroll
+        for (int x = 0; x < D / 64; ++x)
+          tma_load_4d(smem + L::kDO + x * L::kBoxBytes, &tmap_do, &bars[F_DOFULL], x * 64, yh, u * kTile, b);
       }
       __syncwarp();
     }
@@ -229,7 +244,11 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     constexpr uint32_t idesc_dk = make_idesc_bf16(kTile, D, 0, 1);       // dS^T tile (K-major A) x Q (N-major B)
     const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
     const uint32_t kmn_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), L::kBoxBytes);   // K tile with kv as the contraction index
-    const uint32_t ybase = smem_u32(smem + L::kY);
+    const uint32_t qbase = smem_u32(smem + L::kQ);
+    const uint32_t do_k_lo = sdesc_lo_sw128(smem_u32(smem + L::kDO), 16);            // dO, head dimension contracted (dP^T)
+    const uint32_t do_n_lo = sdesc_lo_sw128(smem_u32(smem + L::kDO), L::kBoxBytes);  // dO, queries contracted (dV)
+    const uint32_t ds_addr = smem_u32(smem + L::kDS);
+    const uint32_t ds_mn_lo = sdesc_lo_sw128(ds_addr, L::kBoxBytes), ds_k_lo = sdesc_lo_sw128(ds_addr, 16);
     const int n = __shfl_sync(0xffffffffu, n_items, 0);
     bool ok = true;
     // `tmem_sync`: the barrier orders TMEM loads / stores of other threads before the MMAs that follow; barriers
@@ -247,12 +266,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       }
     };
     wait(F_XFULL, 0, false);
-    if (ok) wait(F_YFULL0, 0, false);
+    if (ok) wait(F_QFULL0, 0, false);
+    if (ok) wait(F_DOFULL, 0, false);
     if (ok) {
       if (elect_one()) {
-        issue_t(tT1, x1_lo, sdesc_lo_sw128(ybase, 16));
+        issue_t(tT1, x1_lo, sdesc_lo_sw128(qbase, 16));
         umma_commit(&bars[F_SFULL]);
-        issue_t(tT2, x2_lo, sdesc_lo_sw128(ybase + L::kTileBytes, 16));
+        issue_t(tT2, x2_lo, do_k_lo);
         umma_commit(&bars[F_DPFULL]);
       }
       __syncwarp();
@@ -261,8 +281,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const uint32_t ph = uint32_t(i & 1);
-      const uint32_t y1 = ybase + st * 2 * L::kTileBytes, y2 = y1 + L::kTileBytes;
-      const uint32_t y1n = ybase + (st ^ 1) * 2 * L::kTileBytes, y2n = y1n + L::kTileBytes;
+      const uint32_t yq = qbase + st * L::kTileBytes, yqn = qbase + (st ^ 1) * L::kTileBytes;
       const uint32_t acc_on = (i > 0) ? 1u : 0u;
       const bool more = (i + 1 < n);
       wait(F_PFULL, ph, true);                                                      // P^T(i) written, S^T(i) consumed
@@ -270,45 +289,42 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       if (!ok) break;
       if (elect_one()) {
         // dV += P^T dO: the half h of the register-math threads wrote its four K-steps at column offset 64 h
-        const uint32_t do_lo = sdesc_lo_sw128(y2, L::kBoxBytes);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts_lo(tDV, tT1 + (kk >> 2) * kSlice + (kk & 3) * 8, do_lo + ((kk * 16 * 128) >> 4), idesc_dv, acc_on | (kk > 0));
-        umma_commit(&bars[F_DVDONE]);                                               // the dO slot may now take dS^T
+          umma_ts_lo(tDV, tT1 + (kk >> 2) * kSlice + (kk & 3) * 8, do_n_lo + ((kk * 16 * 128) >> 4), idesc_dv, acc_on | (kk > 0));
+        umma_commit(&bars[F_DOEMPTY]);                                              // dO(i) is dead: its buffer may take dO(i+1)
       }
       __syncwarp();
       PH(1)
       if (more) {
-        wait(F_YFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
+        wait(F_QFULL0 + (st ^ 1), ((i + 1) >> 1) & 1, false);
         PH(2)
         if (!ok) break;
         if (elect_one()) {
-          issue_t(tT1, x1_lo, sdesc_lo_sw128(y1n, 16));                             // scores of item i+1
+          issue_t(tT1, x1_lo, sdesc_lo_sw128(yqn, 16));                             // scores of item i+1
           umma_commit(&bars[F_SFULL]);
         }
         __syncwarp();
         PH(3)
       }
-      wait(F_DSFULL, ph, true);                                                     // dS^T(i) in the dO slot, dP^T(i) consumed
+      wait(F_DSFULL, ph, true);                                                     // dS^T(i) in its tile, dP^T(i) consumed
       PH(4)
       if (!ok) break;
       if (elect_one()) {
         // dQ(i) = dS K over the dP^T columns: both operands read with kv as the contraction index (16 kv rows per
         // step = 16 lines of 128 bytes)
-        const uint32_t ds_mn_lo = sdesc_lo_sw128(y2, L::kBoxBytes);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
           umma_ss_lo(tT2, ds_mn_lo + ((kk * 16 * 128) >> 4), kmn_lo + ((kk * 16 * 128) >> 4), idesc_dq, kk > 0);
         umma_commit(&bars[F_DQFULL]);
         // dK(i) += dS^T(i) Q(i)
-        const uint32_t ds_k_lo = sdesc_lo_sw128(y2, 16);
-        const uint32_t q_lo = sdesc_lo_sw128(y1, L::kBoxBytes);
+        const uint32_t q_lo = sdesc_lo_sw128(yq, L::kBoxBytes);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;
           umma_ss_lo(tDK, ds_k_lo + off, q_lo + ((kk * 16 * 128) >> 4), idesc_dk, acc_on | (kk > 0));
         }
-        umma_commit(&bars[F_YEMPTY0 + st]);
+        umma_commit(&bars[F_QEMPTY0 + st]);                                         // Q(i) is dead; also: the dS^T tile may be rewritten
         if (!more) umma_commit(&bars[F_ACCFULL]);
       }
       __syncwarp();
@@ -316,9 +332,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       if (more) {
         wait(F_DRAINED, ph, true);                                                  // dQ(i) has left the T2 columns
         PH(6)
+        if (ok) wait(F_DOFULL, uint32_t((i + 1) & 1), false);
         if (!ok) break;
         if (elect_one()) {
-          issue_t(tT2, x2_lo, sdesc_lo_sw128(y2n, 16));                             // dP^T of item i+1
+          issue_t(tT2, x2_lo, do_k_lo);                                             // dP^T of item i+1
           umma_commit(&bars[F_DPFULL]);
         }
         __syncwarp();
@@ -366,27 +383,31 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     };
 
     bool ok = true;
-    uint32_t e_next = __ldg(list);
+    uint32_t e_next = ldg_pinned(list);
     int li = 0;
+    // mask bits of the coming item are worked out one item ahead (in the gap while dP^T of the current item is
+    // awaited), so that their global loads never sit in front of the exponentials
+    uint32_t keep_next[2] = {0xffffffffu, 0xffffffffu};
+    if (e_next & kPartialBit) {
+      const int c0 = int(e_next & ~kPartialBit) * kTile;
+      keep_next[0] = chunk_keep(c0 + cb); keep_next[1] = chunk_keep(c0 + cb + 32);
+    }
+    uint8_t* ds_row = smem + L::kDS + half * L::kBoxBytes + row * 128;   // this thread's 128-byte row of the dS^T tile
     PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
       const uint32_t e = e_next;
       if (++li == count) li = 0;
-      if (i + 1 < n_items) e_next = __ldg(list + li);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+      if (i + 1 < n_items) e_next = ldg_pinned(list + li);
       const bool partial = (e & kPartialBit) != 0;
       const int st = i & 1;
       const uint32_t ph = uint32_t(i & 1);
       const float* cs = s_cols + st * 2 * kTile;
       const float4* cs_lse = reinterpret_cast<const float4*>(cs + cb);
       const float4* cs_dl = reinterpret_cast<const float4*>(cs + kTile + cb);
+      const uint32_t keep[2] = {keep_next[0], keep_next[1]};
 
-      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
-      if (partial) { keep[0] = chunk_keep(c0 + cb); keep[1] = chunk_keep(c0 + cb + 32); }
-
-      PH(0)
-      // LSE2 / delta of this item have landed together with its Q and dO tiles
-      ok = mbar_wait(&bars[F_YFULL0 + st], (i >> 1) & 1, abort_flag, a.status, F_YFULL0 + st);
+      // LSE2 / delta of this item have landed together with its Q tile
+      ok = mbar_wait(&bars[F_QFULL0 + st], (i >> 1) & 1, abort_flag, a.status, F_QFULL0 + st);
       PH(1)
       if (!ok) break;
 
@@ -422,20 +443,29 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       mbar_arrive(&bars[F_PFULL]);
       PH(3)
 
-      // ---- B: dS^T = P^T * (dP^T - delta) -> bf16 -> the shared-memory slot of dO(i), dead once dV(i) has run
+      keep_next[0] = keep_next[1] = 0xffffffffu;
+      if (i + 1 < n_items && (e_next & kPartialBit)) {
+        const int c0n = int(e_next & ~kPartialBit) * kTile;
+        keep_next[0] = chunk_keep(c0n + cb); keep_next[1] = chunk_keep(c0n + cb + 32);
+      }
+      PH(0)
+
+      // ---- B: dS^T = P^T * (dP^T - delta) -> bf16 -> the dS^T tile in shared memory
       ok = mbar_wait(&bars[F_DPFULL], ph, abort_flag, a.status, F_DPFULL);
       PH(4)
       if (!ok) break;
       tc_fence_after();
       uint32_t dp[2][16];                                     // 16 columns at a time, the next request in flight
       tmem_ld16(my_t2, dp[0]);
-      ok = mbar_wait(&bars[F_DVDONE], ph, abort_flag, a.status, F_DVDONE);
+      if (i > 0) {      // dQ(i-1) and dK(i-1), the readers of the tile, have completed (the commit that frees Q stage (i-1) & 1)
+        ok = mbar_wait(&bars[F_QEMPTY0 + ((i - 1) & 1)], ((i - 1) >> 1) & 1, abort_flag, a.status, F_QEMPTY0 + ((i - 1) & 1));
+        if (!ok) break;
+      }
       PH(5)
-      if (!ok) break;
       {
         // kv row `row`, queries [64 half, 64 half + 64) = one 128-byte row of box `half`: eight 16-byte chunks at the
         // positions the 128-byte swizzle assigns them
-        uint8_t* slot = smem + L::kY + st * 2 * L::kTileBytes + L::kTileBytes + half * L::kBoxBytes + row * 128;
+        uint8_t* slot = ds_row;
 #pragma unroll
         for (int sc = 0; sc < 4; ++sc) {                      // columns [16 sc, 16 sc + 16) of this thread's 64
           if (sc + 1 < 4) tmem_ld16(my_t2 + (sc + 1) * 16, dp[(sc + 1) & 1]);
@@ -490,70 +520,64 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     const int dw = warp - kDrainWarp0;                        // = TMEM lane quarter of this warp
     const uint32_t lane_base = uint32_t(dw * 32) << 16;
     uint8_t* stage = smem + L::kStage + dw * 2 * kStageBuf;
+    uint8_t* my_row = stage + lane * 128;                     // this lane's query row in staging buffer 0: 32 fp32, swizzled
     if (lane == 0) prefetch_tmap(&tmap_dq);
     bool ok = true;
-    uint32_t e_next = __ldg(list);
+    uint32_t e_next = ldg_pinned(list);
     int li = 0, qh = kvh * group;
     PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
       const int q0 = int(e_next & ~kPartialBit) * kTile + dw * 32;    // first query row this warp drains
       const int yh = qh;
       if (++li == count) { li = 0; ++qh; }
-      if (i + 1 < n_items) e_next = __ldg(list + li);
+      if (i + 1 < n_items) e_next = ldg_pinned(list + li);
+      const bool live = q0 < q_len;                           // rows beyond the sequence are clipped by TMA; skip all-out boxes
       ok = mbar_wait(&bars[F_DQFULL], uint32_t(i & 1), abort_flag, a.status, F_DQFULL);
       PH(0)
       if (!ok) break;
       tc_fence_after();
       // Registers hold three 32-column chunks at a time (the register file leaves 128 per thread): chunks 0-2 are
-      // requested at once, chunk 0 goes to its staging buffer as soon as it arrives, its registers take chunk 3, and
-      // the T2 columns are released as soon as the last chunk is in registers.
-      const bool live = q0 < q_len;                           // rows beyond the sequence are clipped by TMA; skip all-out boxes
-      auto stage_out = [&](int ch, const uint32_t (&x)[32]) {
-        if (!live) return;
-        uint8_t* buf = stage + (ch & 1) * kStageBuf;
-        if (lane == 0) bulk_wait_group_read<1>();             // the reduce-add issued from this buffer two rounds ago has read it
-        __syncwarp();
-        uint8_t* dst = buf + lane * 128;                      // query row q0 + lane: 32 fp32 = 128 bytes, swizzled
+      // requested at once; chunk 0 is written to its staging buffer as soon as it arrives and chunk 3 is requested
+      // into its registers right behind those stores; the T2 columns are released as soon as all chunks are in
+      // registers, and everything else (proxy fence, reduce-add, the other chunks) happens after that.
+      auto put = [&](int ch, const uint32_t (&x)[32]) {       // registers -> staging buffer ch & 1
+        uint8_t* dst = my_row + (ch & 1) * kStageBuf;
 #pragma unroll
         for (int ck = 0; ck < 8; ++ck)
           *reinterpret_cast<uint4*>(dst + ((ck ^ (lane & 7)) << 4)) = make_uint4(x[4 * ck], x[4 * ck + 1], x[4 * ck + 2], x[4 * ck + 3]);
+      };
+      auto reduce = [&](int ch) {                             // staging buffer ch & 1 -> += accumulator
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_4d(&tmap_dq, buf, ch * 32, yh, q0, b);
+        if (lane == 0 && live) {
+          tma_reduce_add_4d(&tmap_dq, stage + (ch & 1) * kStageBuf, ch * 32, yh, q0, b);
           bulk_commit_group();
         }
       };
-      static_assert(D == 128 || D == 64, "drain schedule written for two or four 32-column chunks");
-      if (D == 128) {
-        uint32_t x0[32], x1[32], x2[32];
-        tmem_ld32(tT2 + lane_base, x0);
-        tmem_ld32(tT2 + lane_base + 32, x1);
-        tmem_ld32(tT2 + lane_base + 64, x2);
-        tmem_ld_wait(x0);
-        stage_out(0, x0);
-        tmem_ld32(tT2 + lane_base + 96, x0);
-        tmem_ld_wait(x1);
-        tmem_ld_wait(x2);
-        tmem_ld_wait(x0);
-        tc_fence_before();
-        mbar_arrive(&bars[F_DRAINED]);                        // the T2 columns may take dP^T(i+1)
-        PH(1)
-        stage_out(1, x1);
-        stage_out(2, x2);
-        stage_out(3, x0);
-        PH(2)
-      } else {
-        uint32_t x0[32], x1[32];
-        tmem_ld32(tT2 + lane_base, x0);
-        tmem_ld32(tT2 + lane_base + 32, x1);
-        tmem_ld_wait(x0);
-        tmem_ld_wait(x1);
-        tc_fence_before();
-        mbar_arrive(&bars[F_DRAINED]);
-        stage_out(0, x0);
-        stage_out(1, x1);
-      }
+      auto buffer_free = [&]() {                              // the reduce-add issued from the buffer two chunks ago has read it
+        if (lane == 0) bulk_wait_group_read<1>();
+        __syncwarp();
+      };
+      static_assert(D == 128, "drain schedule written for four 32-column chunks");
+      uint32_t x0[32], x1[32], x2[32];
+      tmem_ld32(tT2 + lane_base, x0);
+      tmem_ld32(tT2 + lane_base + 32, x1);
+      tmem_ld32(tT2 + lane_base + 64, x2);
+      buffer_free();                                          // buffer 0: chunk 2 of the previous item, long gone
+      tmem_ld_wait(x0);
+      put(0, x0);
+      tmem_ld32(tT2 + lane_base + 96, x0);                    // chunk 3 takes the registers of chunk 0
+      tmem_ld_wait(x1);
+      tmem_ld_wait(x2);
+      tmem_ld_wait(x0);
+      tc_fence_before();
+      mbar_arrive(&bars[F_DRAINED]);                          // the T2 columns may take dP^T(i+1)
+      PH(1)
+      reduce(0);
+      buffer_free(); put(1, x1); reduce(1);
+      buffer_free(); put(2, x2); reduce(2);
+      buffer_free(); put(3, x0); reduce(3);
+      PH(2)
     }
     if (dw == 0) { PH_END(2, n_items) }
     if (lane == 0) bulk_wait_group<0>();                      // all reduce-adds performed before the CTA goes away
@@ -597,6 +621,7 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_cast_kernel(const float* __re
 
 template <int D>
 int launch_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
+  static_assert(D == 128, "the drain is written for four 32-column chunks");
   constexpr int smem = FusedSmem<D>::kTotal;
   auto kern = attn_bwd_fused_kernel<D>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;

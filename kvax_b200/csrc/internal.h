@@ -48,7 +48,8 @@ struct BwdArgs {
   TokenInfo tok;
   const float* lse;         // (B, Hq, Sq) base-2 log-sum-exp from the forward
   const float* delta;       // (B, Hq, Sq) rowsum(O * dO)
-  __nv_bfloat16* dq;        // dQ kernel output, strides q_strides
+  __nv_bfloat16* dq;        // dQ kernel output, strides dq_strides
+  float* dq_acc;            // fused kernel: fp32 dQ accumulator (B, Sq, Hq, D) contiguous, zero on entry
   float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) fp32 contiguous
   float* dv;
   int32_t* status;
