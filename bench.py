@@ -61,30 +61,38 @@ def profile_traffic(kernel: str, workload: str):
     return None, f"no ncu capture of {kernel} on {workload} summarised under profiles/"
 
 
-def tight_tiles(pos, seg):
-    """Tile pairs with at least one unmasked element of segment AND causal AND non-PAD —
-    the work the throughput is normalised by.  Pure NumPy on the host arrays."""
-    B, S = pos.shape
-    n = (S + TILE - 1) // TILE
-    total = 0
+def tile_hits(q_pos, q_seg, kv_pos, kv_seg):
+    """Boolean (B, n_q_tiles, n_kv_tiles): tile pairs with at least one unmasked element of
+    segment AND causal AND non-PAD -- the work the throughput is normalised by.  Exact: a pair holds an
+    allowed element iff for some segment id the largest query position of that segment inside the query
+    tile reaches the smallest kv position of that segment inside the kv tile.  Pure NumPy on host arrays."""
+    B, Sq = q_pos.shape
+    Skv = kv_pos.shape[1]
+    nq, nk = (Sq + TILE - 1) // TILE, (Skv + TILE - 1) // TILE
+    hits = np.zeros((B, nq, nk), dtype=bool)
+
+    def per_tile_segment(pos, seg, reducer, fill):
+        """(tile index, segment id, reduced position) for every (tile, segment) pair that occurs; PAD left out."""
+        idx = np.nonzero(seg != -1)[0]
+        tile = idx // TILE
+        key = tile.astype(np.int64) * (1 << 32) + seg[idx].astype(np.int64)
+        uniq, inv = np.unique(key, return_inverse=True)
+        red = np.full(len(uniq), fill, dtype=np.int64)
+        reducer.at(red, inv, pos[idx].astype(np.int64))
+        return (uniq >> 32).astype(np.int64), (uniq & 0xffffffff).astype(np.int64), red
+
     for b in range(B):
-        p, s = pos[b], seg[b]
-        pt = np.pad(p, (0, n * TILE - S), constant_values=np.iinfo(np.int32).max).reshape(n, TILE)
-        st = np.pad(s, (0, n * TILE - S), constant_values=-1).reshape(n, TILE)
-        for qi in range(n):
-            qp, qs = pt[qi], st[qi]
-            valid_q = qs != -1
-            if not valid_q.any():
-                continue
-            # only kv tiles whose segment range overlaps can match; test those exactly
-            smin, smax = qs[valid_q].min(), qs[valid_q].max()
-            kmin = np.where(st == -1, np.iinfo(np.int32).max, st).min(1)
-            kmax = st.max(1)
-            cand = np.nonzero((kmin <= smax) & (kmax >= smin))[0]
-            for kj in cand:
-                m = (qs[:, None] == st[kj][None, :]) & (qp[:, None] >= pt[kj][None, :]) & valid_q[:, None] & (st[kj] != -1)[None, :]
-                total += bool(m.any())
-    return total
+        qt, qs, qmax = per_tile_segment(q_pos[b], q_seg[b], np.maximum, np.iinfo(np.int64).min)
+        kt, ks, kmin = per_tile_segment(kv_pos[b], kv_seg[b], np.minimum, np.iinfo(np.int64).max)
+        for s in np.intersect1d(qs, ks):
+            qi, ki = np.nonzero(qs == s)[0], np.nonzero(ks == s)[0]
+            hits[b][np.ix_(qt[qi], kt[ki])] |= qmax[qi][:, None] >= kmin[ki][None, :]
+    return hits
+
+
+def tight_tiles(pos, seg):
+    """Number of unmasked tile pairs of a self-attention layout (see `tile_hits`)."""
+    return int(tile_hits(pos, seg, pos, seg).sum())
 
 
 class ClockSampler:
@@ -184,6 +192,52 @@ def cpu_dense_sample(cfg, inp, seconds_target=12.0):
     return flops / sec / 1e12, sample, sec, cores
 
 
+def same_gpu_reference(q, k, v, do, pos, seg, scale, flops_fwd):
+    """Times kvax's unmodified Triton kernels (host functions included) on this GPU on the step's own
+    tensors: oracle/triton_reference.py, H100 launch setting of the reference (forward 128 x 128,
+    backward 64 x 128 tiles, 8 warps, 3 stages or fewer if shared memory does not suffice).  Returns
+    the dict for the JSON line, or {"unavailable": reason}."""
+    try:
+        from oracle import triton_reference as tr
+        ok, why = tr.available()
+        if not ok:
+            return {"unavailable": why}
+        from kvax_b200.ops.mask_creator import build_masks
+        fwd, bwd = (128, 128), (64, 128)
+        masks = tr.mask_tuple(build_masks(pos, seg, pos, seg, [(fwd[0], fwd[1], False), (bwd[1], bwd[0], False),
+                                                                (bwd[0], bwd[1], True)], True))
+        q_t, k_t, v_t, do_t = (tr.to_bhsd(x) for x in (q, k, v, do))
+        last = None
+        for stages in (3, 2, 1):
+            try:
+                fp, bp = tr.params(*fwd, num_warps=8, num_stages=stages), tr.params(*bwd, num_warps=8, num_stages=stages)
+                out_t, res = tr.launch_forward(q_t, k_t, v_t, pos, seg, pos, seg, masks, scale, fp, bp)
+                tr.launch_backward(res, do_t, scale, fp, bp)
+                torch.cuda.synchronize()
+                break
+            except Exception as e:
+                if "out of resource" not in str(e).lower() and "shared memory" not in str(e).lower():
+                    raise
+                last = e
+        else:
+            return {"unavailable": f"Triton could not fit the reference's tiles: {last}"}
+        holder = {}
+
+        def f():
+            holder["res"] = tr.launch_forward(q_t, k_t, v_t, pos, seg, pos, seg, masks, scale, fp, bp)[1]
+
+        fwd_ms = cuda_time(f, 3)
+        bwd_ms = cuda_time(lambda: tr.launch_backward(holder["res"], do_t, scale, fp, bp), 3)
+        return {"fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "ms_per_step": fwd_ms + bwd_ms, "unit": UNIT,
+                "value": 3.5 * flops_fwd / ((fwd_ms + bwd_ms) * 1e-3) / 1e12,
+                "fwd_tflops": flops_fwd / (fwd_ms * 1e-3) / 1e12, "bwd_tflops": 2.5 * flops_fwd / (bwd_ms * 1e-3) / 1e12,
+                "what": "kvax flash_attention_triton_forward + flash_attention_backward (host code + Triton kernels), "
+                        f"fwd tiles {fwd}, bwd tiles {bwd}, 8 warps, {stages} stages, Triton of this image; block masks prebuilt; "
+                        "same tensors, same FLOP count as `value`"}
+    except Exception as e:          # the comparator must never take the benchmark down
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -223,7 +277,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kvax_b200", choices=["kvax_b200", "reference"])
     ap.add_argument("--workload", default=None, help="override the configuration (c2_llama8b_8k, c3_dense_causal_16k, ...)")
+    ap.add_argument("--no-other-schedule", action="store_true",
+                    help="with --gpus N > 1: do not also time the all-gather schedule")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-same-gpu-reference", action="store_true",
+                    help="skip timing the reference's own Triton kernels on this GPU (single-GPU runs)")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -264,50 +322,61 @@ def main():
     kv.set_context_parallel_mode(args.cp_mode)
     hx = cp > 1 and Hkv % cp == 0 and args.cp_mode != "all_gather"
 
-    # ---- the same workload on ONE GPU (rank 0, before the context-parallel run): the N = 1 line of a scaling
-    # series uses the metric's own 32k configuration, so the strong-scaling reference for this workload is
-    # measured here and reported beside the aggregate.
-    same_1gpu = None
-    if cp > 1 and not args.no_single_gpu_reference:
-        if rank == 0:
-            g1 = torch.Generator(device=dev).manual_seed(99)
-            r1 = lambda *shape: torch.randn(*shape, generator=g1, device=dev, dtype=torch.float32).to(torch.bfloat16)
-            q1, k1, v1, do1 = r1(B, S, Hq, D), r1(B, S, Hkv, D), r1(B, S, Hkv, D), r1(B, S, Hq, D)
-            p1, s1 = torch.from_numpy(pos_h).to(dev), torch.from_numpy(seg_h).to(dev)
-            spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
-
-            def one_gpu_step():
-                m = build_masks(p1, s1, p1, s1, spec3, True)
-                o1, l1, _ = attention_forward(q1, k1, v1, p1, s1, p1, s1, m[0], (TILE, TILE), scale)
-                attention_backward(q1, k1, v1, o1, do1, l1, p1, s1, p1, s1, m[1], m[2], (TILE, TILE), scale)
-
-            for _ in range(2):
-                one_gpu_step()
-            ms1 = cuda_time(one_gpu_step, 3)
-            same_1gpu = {"workload": cfg.name, "n_gpus": 1, "ms_per_step": ms1, "value": flops_step / (ms1 * 1e-3) / 1e12,
-                         "unit": UNIT, "steps": 3}
-            del q1, k1, v1, do1, p1, s1
-            torch.cuda.empty_cache()
-        dist.barrier()
+    # ---- N > 1: every rank draws the SAME full tensors (seeded), runs the whole workload alone on its own GPU -- the
+    # one-GPU time of this workload, which the N = 1 line of a scaling series (the 32k configuration) does not give,
+    # and the reference values of the numeric check -- and then keeps its slice of the permuted sequence.
+    same_1gpu, single = None, None
     mesh = kv.Mesh(("data", "context"), (1, cp))
     q_spec = ("data", "context" if cp > 1 else None, None, None)
     kv_spec = ("data", None, None, None)
     S_loc = S // cp
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    kv_pos = torch.from_numpy(pos_h).to(dev); kv_seg = torch.from_numpy(seg_h).to(dev)
+    g = torch.Generator(device=dev).manual_seed(1234)
 
     def randn(*shape):
         return torch.randn(*shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
 
-    q = randn(B, S_loc, Hq, D); k = randn(B, S_loc, Hkv, D); v = randn(B, S_loc, Hkv, D); do = randn(B, S_loc, Hq, D)
-    kv_pos = torch.from_numpy(pos_h).to(dev); kv_seg = torch.from_numpy(seg_h).to(dev)
-    with mesh, kv.attention_specs(q_spec, kv_spec):
-        if cp > 1:   # the caller permutes the query side, every rank keeps its slice
-            qp_full, qs_full = kv.permute_tokens_context_parallelism((kv_pos, kv_seg))
-            q_pos = qp_full[:, rank * S_loc:(rank + 1) * S_loc].contiguous()
-            q_seg = qs_full[:, rank * S_loc:(rank + 1) * S_loc].contiguous()
-        else:
-            q_pos, q_seg = kv_pos, kv_seg
+    per_rank_tiles = None
+    if cp > 1:
+        qf, kf, vf, dof = randn(B, S, Hq, D), randn(B, S, Hkv, D), randn(B, S, Hkv, D), randn(B, S, Hq, D)
+        if not args.no_single_gpu_reference:
+            spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
 
+            def one_gpu_step():
+                m = build_masks(kv_pos, kv_seg, kv_pos, kv_seg, spec3, True)
+                o1, l1, _ = attention_forward(qf, kf, vf, kv_pos, kv_seg, kv_pos, kv_seg, m[0], (TILE, TILE), scale)
+                g1 = attention_backward(qf, kf, vf, o1, dof, l1, kv_pos, kv_seg, kv_pos, kv_seg, m[1], m[2], (TILE, TILE), scale)
+                return o1, g1[0], g1[1], g1[2]
+
+            for _ in range(2):
+                one_gpu_step()
+            ms1 = cuda_time(one_gpu_step, 3)
+            t1 = torch.tensor([ms1], device=dev)
+            dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+            ms1 = float(t1.item())
+            same_1gpu = {"workload": cfg.name, "n_gpus": 1, "ms_per_step": ms1, "value": flops_step / (ms1 * 1e-3) / 1e12,
+                         "unit": UNIT, "steps": 3, "note": "every rank alone on its own GPU, max over ranks"}
+            single = one_gpu_step()
+        with mesh, kv.attention_specs(q_spec, kv_spec):
+            sl = slice(rank * S_loc, (rank + 1) * S_loc)
+            take = lambda x: kv.permute_tokens_context_parallelism(x)[:, sl].contiguous()
+            q, k, v, do = take(qf), take(kf), take(vf), take(dof)
+            q_pos, q_seg = take(kv_pos), take(kv_seg)
+            if single is not None:      # slices of the one-GPU results this rank must reproduce
+                single = tuple(take(x) for x in single)
+        del qf, kf, vf, dof
+        torch.cuda.empty_cache()
+        if rank == 0:                    # unmasked tile pairs of every rank's local queries against all keys (all-gather schedule)
+            perm = np.concatenate([np.arange(c * (S // (2 * cp)), (c + 1) * (S // (2 * cp)))
+                                   for c in sum(([i, 2 * cp - 1 - i] for i in range(cp)), [])])
+            hits = tile_hits(pos_h[:, perm], seg_h[:, perm], pos_h, seg_h)
+            per_q_tile = hits.sum(axis=(0, 2))
+            tiles_loc = S_loc // TILE
+            per_rank_tiles = [int(per_q_tile[r * tiles_loc:(r + 1) * tiles_loc].sum()) for r in range(cp)]
+    else:
+        q = randn(B, S_loc, Hq, D); k = randn(B, S_loc, Hkv, D); v = randn(B, S_loc, Hkv, D); do = randn(B, S_loc, Hq, D)
+        q_pos, q_seg = kv_pos, kv_seg
+    with mesh, kv.attention_specs(q_spec, kv_spec):
         q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
 
         def step():
@@ -343,6 +412,52 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms_total = float(t.item())
         ms_step = ms_total / K
+
+        # ---- N > 1: numeric check against the one-GPU run of the same tensors, and the other schedule ---------------
+        cp_check, other_schedule = None, None
+        if cp > 1:
+            def run_once():
+                for t_ in (q, k, v):
+                    t_.grad = None
+                masks_ = kv.create_attention_mask(q_pos, q_seg, kv_pos, kv_seg, fwd_params=params, bwd_params=params,
+                                                  calc_bwd_mask=True)
+                o_ = kv.flash_attention(q, k, v, q_pos, q_seg, kv_pos, kv_seg, masks_, scale=scale, fwd_params=params,
+                                        bwd_params=params)
+                o_.backward(do)
+                return o_.detach(), q.grad, k.grad, v.grad
+
+            def check(results):
+                rows = (q_seg != -1)[:, :, None, None]
+                errs, refs = [], []
+                for got, ref in zip(results, single):
+                    g_ = torch.where(rows, got.float(), torch.zeros((), device=dev))
+                    r_ = torch.where(rows, ref.float(), torch.zeros((), device=dev))
+                    errs.append((g_ - r_).abs().max())
+                    refs.append(r_.abs().max())
+                e_ = torch.stack(errs + refs)
+                dist.all_reduce(e_, op=dist.ReduceOp.MAX)
+                e_ = [float(x) for x in e_]
+                names = ("out", "dq", "dk", "dv")
+                return {"max_abs": dict(zip(names, e_[:4])), "ref_max": dict(zip(names, e_[4:])),
+                        "against": "the one-GPU run of the same seeded tensors, each rank its own slice, max over ranks, non-PAD rows"}
+
+            if single is not None:
+                cp_check = {("head_exchange" if hx else "all_gather"): check(run_once())}
+            if hx and not args.no_other_schedule:     # the schedule the reference has: K/V all-gather, dK/dV reduce-scatter
+                kv.set_context_parallel_mode("all_gather")
+                for _ in range(2):
+                    run_once()
+                if single is not None:
+                    cp_check["all_gather"] = check(run_once())
+                ms_ag = cuda_time(step, 3)
+                t = torch.tensor([ms_ag], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms_ag = float(t.item())
+                other_schedule = {"parallelism": f"cp{cp}:all_gather", "ms_per_step": ms_ag, "steps": 3,
+                                  "value": flops_step / (ms_ag * 1e-3) / 1e12, "unit": UNIT}
+                kv.set_context_parallel_mode(args.cp_mode)
+            single = None
+            torch.cuda.empty_cache()
 
         # ---- per-kernel timing for the roofline (single GPU leg only) ------------------
         roofline, parts = None, {}
@@ -391,22 +506,34 @@ def main():
                         "step_frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
                         "step_frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / 2250.0}
 
+        # ---- the reference's own Triton kernels on this GPU, same inputs (comparator; not part of the timed step)
+        same_gpu_ref = None
+        if cp == 1 and not args.no_same_gpu_reference:
+            same_gpu_ref = same_gpu_reference(q.detach(), k.detach(), v.detach(), do, q_pos, q_seg, scale, flops_fwd)
+
         # ---- mask builder at a size where bandwidth is measurable (the benchmark
         #      configurations are <= 2 MiB, i.e. launch bound) -----------------------------
         mask_info = None
         if cp == 1:
-            from kvax_b200.ops.mask_creator import build_masks
+            from kvax_b200.ops.mask_creator import MaskPlan
             spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
-            mask_info = {"at_workload_us": parts.get("mask_build_ms", 0.0) * 1e3}
+            # `at_workload_us`: the public call (host work + launch) on the step's own arrays; `kernel_us`: the kernel
+            # alone through a prepared call.  The benchmark configurations are <= 2 MiB of input, i.e. latency bound;
+            # bandwidth is measured on two larger synthetic layouts.
+            plan = MaskPlan(q_pos, q_seg, kv_pos, kv_seg, spec3, True)
+            plan.launch()
+            mask_info = {"at_workload_us": parts.get("mask_build_ms", 0.0) * 1e3,
+                         "at_workload_kernel_us": cuda_time(plan.launch, 50) * 1e3}
             for (mb, ms_) in ((2048, 4096), (64, 131072)):
                 mp = (torch.arange(ms_, device=dev, dtype=torch.int32) % 1000).repeat(mb, 1)
                 msg = (torch.arange(ms_, device=dev, dtype=torch.int32) // 1000).repeat(mb, 1)
-                build_masks(mp, msg, mp, msg, spec3, True)
-                t_ms = cuda_time(lambda: build_masks(mp, msg, mp, msg, spec3, True), 10)
+                plan = MaskPlan(mp, msg, mp, msg, spec3, True)
+                plan.launch()
+                t_ms = cuda_time(plan.launch, 20)
                 alg = 16.0 * mb * ms_ + 48.0 * mb * ms_ / TILE
                 mask_info[f"B{mb}_S{ms_}"] = {"ms": t_ms, "algorithmic_GBps": alg / (t_ms * 1e-3) / 1e9,
                                               "frac_of_hbm": alg / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-                del mp, msg
+                del mp, msg, plan
 
         # ---- end to end: pinned host buffers in, results back out, every step ----------
         e2e = None
@@ -506,6 +633,19 @@ def main():
         line["mask_builder"] = mask_info
     if same_1gpu:
         line["same_workload_1gpu"] = same_1gpu
+        line["same_workload_efficiency"] = same_1gpu["ms_per_step"] / (cp * ms_step)
+    if cp > 1:
+        line["cp_check"] = cp_check
+        if per_rank_tiles:
+            mean = sum(per_rank_tiles) / len(per_rank_tiles)
+            line["all_gather_tiles_per_rank"] = {"unmasked_tile_pairs": per_rank_tiles, "max_over_mean": max(per_rank_tiles) / mean,
+                                                 "efficiency_cap": mean / max(per_rank_tiles)}
+        if other_schedule:
+            if same_1gpu:
+                other_schedule["same_workload_efficiency"] = same_1gpu["ms_per_step"] / (cp * other_schedule["ms_per_step"])
+            line["all_gather_schedule"] = other_schedule
+    if cp == 1 and same_gpu_ref is not None:
+        line["same_gpu_reference"] = same_gpu_ref
     if e2e:
         line["e2e"] = e2e
     if cp == 1 and not args.no_cpu_baseline:

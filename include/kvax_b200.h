@@ -126,6 +126,15 @@ int kvax_b200_mask_build_static(const kvax_b200_mask_params* p, kvax_b200_stream
 int kvax_b200_permute_tokens(const void* src, void* dst, int64_t batch, int64_t seq_len, int64_t row_bytes,
                              int32_t cp, int32_t reverse, kvax_b200_stream_t stream);
 
+/* Head regrouping for the head-exchange schedule of context parallelism (no counterpart in
+ * the reference, which only has the all-gather schedule, flash_attention_triton.py:2107-2154):
+ * one pass from (tokens, cp * heads_per_group, D) to the all-to-all send layout
+ * (cp, tokens, heads_per_group, D) -- group r holds the heads rank r will own -- or back
+ * (to_groups = 0).  `tokens` = batch * local sequence length, `head_bytes` = D * element size,
+ * a multiple of 16; both pointers 16-byte aligned. */
+int kvax_b200_regroup_heads(const void* src, void* dst, int64_t tokens, int32_t cp, int32_t heads_per_group,
+                            int64_t head_bytes, int32_t to_groups, kvax_b200_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Flash attention, forward and backward.
  * ---------------------------------------------------------------------------------- */

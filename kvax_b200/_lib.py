@@ -17,6 +17,7 @@ EXPORTS = (
     "kvax_b200_mask_build",
     "kvax_b200_mask_build_static",
     "kvax_b200_permute_tokens",
+    "kvax_b200_regroup_heads",
     "kvax_b200_attn_fwd_workspace_bytes",
     "kvax_b200_attn_fwd",
     "kvax_b200_attn_bwd_workspace_bytes",
@@ -94,6 +95,8 @@ def load() -> C.CDLL:
     lib.kvax_b200_mask_build_static.argtypes = [C.POINTER(MaskParams), vp]
     lib.kvax_b200_permute_tokens.restype = C.c_int
     lib.kvax_b200_permute_tokens.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp]
+    lib.kvax_b200_regroup_heads.restype = C.c_int
+    lib.kvax_b200_regroup_heads.argtypes = [vp, vp, i64, i32, i32, i64, i32, vp]
     lib.kvax_b200_attn_fwd_workspace_bytes.restype = C.c_size_t
     lib.kvax_b200_attn_fwd_workspace_bytes.argtypes = [C.POINTER(AttnFwdParams)]
     lib.kvax_b200_attn_fwd.restype = C.c_int

@@ -1,6 +1,19 @@
 // Block-mask builder for sm_100a.
 //
-// Two launches build up to three masks (forward, dq, dkdv):
+// Main path: ONE launch of thread-block clusters builds up to three masks (forward, dq, dkdv).  A
+// cluster of up to 8 CTAs owns one batch row.  Every CTA summarises its slice of the row's blocks
+// (one warp per block: coalesced 16-byte loads of positions and segment ids, warp min/max, one int4
+// {seg_min, seg_max, pos_min, pos_max} per block, PAD already remapped) into its own shared memory,
+// plus one summary per group of 32 blocks; sides that several masks share (same block size and PAD
+// id) are summarised once, so the inputs are read from HBM exactly once.  After a cluster barrier
+// every warp takes outer blocks of its slice and finds the four bounds by reading the other CTAs'
+// summaries through distributed shared memory: the group summaries rule out whole groups of 32 inner
+// blocks at a time, and only the first / last groups that can hold a hit are looked at block by
+// block.  Masks with identical geometry (forward and dq at equal block sizes) are computed once and
+// stored twice.  Nothing goes through global scratch memory.
+//
+// Fallback (rows whose summaries do not fit in shared memory, and the variant with built-in scratch
+// memory): two launches,
 //   1. mask_summary_kernel: one warp per block of either side; coalesced 16-byte loads of
 //      positions and segment ids, warp min/max reductions, one int4 summary
 //      {seg_min, seg_max, pos_min, pos_max} per block (PAD already remapped).
@@ -10,11 +23,14 @@
 //
 // Semantics follow kvax/ops/mask_creator.py:26-152 (kernel) and :212-259, :317-333 (host
 // steps) exactly; outputs are bit-identical with the reference's mask tensors.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <limits.h>
 
 #include "../../include/kvax_b200.h"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -165,6 +181,354 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) mask_bounds_kernel(const 
 inline int cdiv(long long a, long long b) { return int((a + b - 1) / b); }
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// ---------------------------------------------------------------------------------------
+// Cluster path
+// ---------------------------------------------------------------------------------------
+constexpr int kMaxSets = 6;             // distinct (side, block size, PAD id) combinations of three masks
+constexpr int kClusterThreads = 512;
+constexpr int kGroup = 32;              // inner blocks per group summary
+
+struct SetDesc {
+  const int32_t* pos;
+  const int32_t* seg;
+  int32_t len, block, n_blocks;
+  int32_t pos_fill, pad_id;
+  int32_t per;             // blocks per CTA of the cluster (a multiple of kGroup)
+  int32_t smem_off;        // int4 offset of this set's summaries in a CTA's shared memory; group summaries follow
+  int32_t row_off;         // int4 offset of the CTA's private copy of the whole row's summaries (cluster * per
+                           // block summaries, then cluster * per / kGroup group summaries), or -1: read remotely
+};
+
+struct ClusterMask {
+  int32_t* lower; int32_t* upper; int32_t* lower_full; int32_t* upper_full;
+  int32_t outer_set, inner_set, kv_outer;
+  int32_t same_as;         // index of an earlier mask with the same geometry (its results are stored here too), or -1
+};
+
+struct ClusterArgs {
+  SetDesc sets[kMaxSets];
+  ClusterMask masks[3];
+  int32_t n_sets, n_masks, batch, skip_pad, cluster;
+};
+
+__device__ __forceinline__ int4 warp_reduce_summary(int4 v) {
+  v.x = __reduce_min_sync(0xffffffffu, v.x);
+  v.y = __reduce_max_sync(0xffffffffu, v.y);
+  v.z = __reduce_min_sync(0xffffffffu, v.z);
+  v.w = __reduce_max_sync(0xffffffffu, v.w);
+  return v;
+}
+
+// Summary of block `blk` of batch row `row_off` of one side; whole warp.
+__device__ __forceinline__ int4 block_summary(const SetDesc& sd, long long row_off, int blk, int lane) {
+  const int start = blk * sd.block;
+  const int end = min(start + sd.block, sd.len);
+  int smin = INT_MAX, smax = INT_MIN, pmin = INT_MAX, pmax = INT_MIN;
+  const int32_t* pos = sd.pos + row_off;
+  const int32_t* seg = sd.seg + row_off;
+  const bool vec_ok = (((reinterpret_cast<uintptr_t>(pos + start) | reinterpret_cast<uintptr_t>(seg + start)) & 15) == 0);
+  int i = start;
+  if (vec_ok) {
+    const int n4 = (end - start) >> 2;
+    const int4* p4 = reinterpret_cast<const int4*>(pos + start);
+    const int4* s4 = reinterpret_cast<const int4*>(seg + start);
+    for (int v = lane; v < n4; v += 32) {
+      const int4 p = __ldg(p4 + v);
+      const int4 q = __ldg(s4 + v);
+      fold(p.x, q.x, sd.pad_id, smin, smax, pmin, pmax);
+      fold(p.y, q.y, sd.pad_id, smin, smax, pmin, pmax);
+      fold(p.z, q.z, sd.pad_id, smin, smax, pmin, pmax);
+      fold(p.w, q.w, sd.pad_id, smin, smax, pmin, pmax);
+    }
+    i = start + (n4 << 2);
+  }
+  for (int e = i + lane; e < end; e += 32) fold(__ldg(pos + e), __ldg(seg + e), sd.pad_id, smin, smax, pmin, pmax);
+  if (end < start + sd.block && lane == 0)            // elements added by padding to the block size (mask_creator.py:212-225)
+    fold(sd.pos_fill, KVAX_B200_PADDING_SEGMENT_ID, sd.pad_id, smin, smax, pmin, pmax);
+  return warp_reduce_summary(make_int4(smin, smax, pmin, pmax));
+}
+
+// "may attend" / "fully attends" of outer block o against inner block s (mask_creator.py:98-139)
+__device__ __forceinline__ void block_tests(const int4& o, bool o_single, const int4& s, bool kv_outer, bool skip_pad, int pad_id,
+                                            bool* attend, bool* full) {
+  const bool seg_overlap = (s.x <= o.y) && (o.x <= s.y);
+  const bool both_single = o_single && (s.x == s.y);
+  bool pos_any, pos_all;
+  if (!kv_outer) { pos_any = o.w >= s.z; pos_all = o.z >= s.w; }
+  else           { pos_any = s.w >= o.z; pos_all = s.z >= o.w; }
+  bool att = pos_any && seg_overlap;
+  if (skip_pad) att = att && (s.x != pad_id);
+  *attend = att;
+  *full = both_single && pos_all && att;
+}
+
+__global__ void __launch_bounds__(kClusterThreads) mask_cluster_kernel(const ClusterArgs a) {
+  extern __shared__ int4 sm[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int c = int(cluster.block_rank());
+  const int b = blockIdx.x / a.cluster;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps = kClusterThreads / 32;
+
+  // ---- phase 1: summaries of this CTA's slice of every set, then one summary per group of 32 blocks
+  for (int si = 0; si < a.n_sets; ++si) {
+    const SetDesc& sd = a.sets[si];
+    int4* sum = sm + sd.smem_off;
+    const int first = c * sd.per;
+    const long long row_off = (long long)b * sd.len;
+    // Fast path: blocks of at most 128 tokens whose first element is 16-byte aligned are one int4 per lane and
+    // array; a warp then takes four blocks per step with all eight loads in flight before the first reduction.
+    const bool fast = sd.block <= 128 && (sd.block & 3) == 0 &&
+                      (((reinterpret_cast<uintptr_t>(sd.pos + row_off) | reinterpret_cast<uintptr_t>(sd.seg + row_off)) & 15) == 0);
+    if (fast) {
+      const int n4 = sd.block >> 2;
+      for (int k0 = warp * 4; k0 < sd.per; k0 += kWarps * 4) {
+        int4 pv[4], sv[4];
+        bool have[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int blk = first + k0 + j;
+          const int e0 = blk * sd.block + lane * 4;                  // first of this lane's four tokens
+          have[j] = (k0 + j < sd.per) && (blk < sd.n_blocks) && (lane < n4) && (e0 + 4 <= sd.len);
+          if (have[j]) {
+            pv[j] = __ldg(reinterpret_cast<const int4*>(sd.pos + row_off + e0));
+            sv[j] = __ldg(reinterpret_cast<const int4*>(sd.seg + row_off + e0));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int blk = first + k0 + j;
+          if (k0 + j >= sd.per) break;
+          int smin = INT_MAX, smax = INT_MIN, pmin = INT_MAX, pmax = INT_MIN;
+          if (blk < sd.n_blocks) {
+            if (have[j]) {
+              fold(pv[j].x, sv[j].x, sd.pad_id, smin, smax, pmin, pmax);
+              fold(pv[j].y, sv[j].y, sd.pad_id, smin, smax, pmin, pmax);
+              fold(pv[j].z, sv[j].z, sd.pad_id, smin, smax, pmin, pmax);
+              fold(pv[j].w, sv[j].w, sd.pad_id, smin, smax, pmin, pmax);
+            } else if (lane < n4) {                                   // the block is cut by the end of the row
+              const int e0 = blk * sd.block + lane * 4;
+              for (int e = e0; e < min(e0 + 4, sd.len); ++e)
+                fold(__ldg(sd.pos + row_off + e), __ldg(sd.seg + row_off + e), sd.pad_id, smin, smax, pmin, pmax);
+            }
+            if (blk * sd.block + sd.block > sd.len && lane == 0)      // elements added by padding to the block size
+              fold(sd.pos_fill, KVAX_B200_PADDING_SEGMENT_ID, sd.pad_id, smin, smax, pmin, pmax);
+          }
+          const int4 v = warp_reduce_summary(make_int4(smin, smax, pmin, pmax));
+          if (lane == 0) sum[k0 + j] = v;
+        }
+      }
+    } else {
+      for (int k = warp; k < sd.per; k += kWarps) {
+        const int blk = first + k;
+        int4 v = make_int4(INT_MAX, INT_MIN, INT_MAX, INT_MIN);     // beyond the row: matches nothing
+        if (blk < sd.n_blocks) v = block_summary(sd, row_off, blk, lane);
+        if (lane == 0) sum[k] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int si = 0; si < a.n_sets; ++si) {
+    const SetDesc& sd = a.sets[si];
+    const int4* sum = sm + sd.smem_off;
+    int4* grp = sm + sd.smem_off + sd.per;
+    for (int g = warp; g < sd.per / kGroup; g += kWarps) {
+      const int4 v = warp_reduce_summary(sum[g * kGroup + lane]);
+      if (lane == 0) grp[g] = v;
+    }
+  }
+  cluster.sync();
+
+  // ---- every CTA takes a private copy of the whole row's summaries (when they fit): the scans below then only
+  //      touch local shared memory and the CTAs of the cluster need each other no longer
+  bool all_local = true;
+  for (int si = 0; si < a.n_sets; ++si) {
+    const SetDesc& sd = a.sets[si];
+    if (sd.row_off < 0) { all_local = false; continue; }
+    int4* base = sm + sd.smem_off;
+    int4* row = sm + sd.row_off;
+    const int total = a.cluster * sd.per, gper = sd.per / kGroup;
+    for (int idx = threadIdx.x; idx < total; idx += kClusterThreads) {
+      const int rank = idx / sd.per;
+      row[idx] = *(cluster.map_shared_rank(base, rank) + (idx - rank * sd.per));
+    }
+    for (int idx = threadIdx.x; idx < a.cluster * gper; idx += kClusterThreads) {
+      const int rank = idx / gper;
+      row[total + idx] = *(cluster.map_shared_rank(base, rank) + sd.per + (idx - rank * gper));
+    }
+  }
+  if (all_local) cluster.sync(); else __syncthreads();
+
+  // ---- phase 2: bounds of the outer blocks of this CTA's slice
+  for (int m = 0; m < a.n_masks; ++m) {
+    const ClusterMask& mk = a.masks[m];
+    if (mk.same_as >= 0) continue;                                  // stored together with the mask it equals
+    const SetDesc& so = a.sets[mk.outer_set];
+    const SetDesc& si = a.sets[mk.inner_set];
+    const int n = si.n_blocks, n_groups = (n + kGroup - 1) / kGroup;
+    const int groups_per_cta = si.per / kGroup;
+    const bool kv_outer = mk.kv_outer != 0, skip_pad = a.skip_pad != 0;
+    const int pad_id = so.pad_id;
+    const int4* o_sum = sm + so.smem_off;
+    int4* in_base = sm + si.smem_off;
+    const int4* in_row = si.row_off >= 0 ? sm + si.row_off : nullptr;
+    const int in_total = a.cluster * si.per;
+    auto inner_at = [&](int i) -> int4 {                            // summary of inner block i, wherever it lives
+      if (in_row) return in_row[i];
+      const int rank = i / si.per;
+      return *(cluster.map_shared_rank(in_base, rank) + (i - rank * si.per));
+    };
+    auto group_at = [&](int g) -> int4 {
+      if (in_row) return in_row[in_total + g];
+      const int rank = g / groups_per_cta;
+      return *(cluster.map_shared_rank(in_base, rank) + si.per + (g - rank * groups_per_cta));
+    };
+    for (int k = warp; k < so.per; k += kWarps) {
+      const int ob = c * so.per + k;
+      if (ob >= so.n_blocks) break;
+      const int4 o = o_sum[k];
+      const bool o_single = (o.x == o.y);
+      int lo = n, up = 0, lof = n, upf = 0;
+      const bool outer_all_pad = skip_pad && o_single && (o.x == pad_id);              // :69-76
+      if (!outer_all_pad) {
+        // A group summary passes the interval tests whenever one of its members does (the PAD test is left to the
+        // members: it is not monotone under min / max).  `full` needs a single-segment outer block.
+        auto group_candidates = [&](int g0) -> unsigned {
+          const int g = g0 + lane;
+          bool cand = false;
+          if (g < n_groups) {
+            bool ful;
+            block_tests(o, o_single, group_at(g), kv_outer, false, pad_id, &cand, &ful);
+          }
+          return __ballot_sync(0xffffffffu, cand);
+        };
+        // ascending over the groups that can hold a hit: first `attend` -> lower, first `full` -> lower_full
+        const bool one_step = n_groups <= 32;                       // the usual case: the candidate mask is computed once
+        const unsigned cand0 = one_step ? group_candidates(0) : 0u;
+        bool lo_done = false, lof_done = !o_single;
+        for (int g0 = 0; g0 < n_groups && !(lo_done && lof_done); g0 += 32) {
+          unsigned rest = one_step ? cand0 : group_candidates(g0);
+          while (rest && !(lo_done && lof_done)) {
+            const int gi = g0 + __ffs(rest) - 1;
+            rest &= rest - 1;
+            const int i = gi * kGroup + lane;
+            bool att = false, ful = false;
+            if (i < n) block_tests(o, o_single, inner_at(i), kv_outer, skip_pad, pad_id, &att, &ful);
+            const unsigned am = __ballot_sync(0xffffffffu, att), fm = __ballot_sync(0xffffffffu, ful);
+            if (!lo_done && am) { lo = gi * kGroup + __ffs(am) - 1; lo_done = true; }
+            if (!lof_done && fm) { lof = gi * kGroup + __ffs(fm) - 1; lof_done = true; }
+          }
+        }
+        // descending: last `attend` -> upper, last `full` -> upper_full (none of either if the ascending pass found none)
+        bool up_done = !lo_done, upf_done = !(o_single && lof != n);
+        for (int g0 = ((n_groups - 1) / 32) * 32; g0 >= 0 && !(up_done && upf_done); g0 -= 32) {
+          unsigned rest = one_step ? cand0 : group_candidates(g0);
+          while (rest && !(up_done && upf_done)) {
+            const int bit = 31 - __clz(rest);
+            rest &= ~(1u << bit);
+            const int gi = g0 + bit;
+            const int i = gi * kGroup + lane;
+            bool att = false, ful = false;
+            if (i < n) block_tests(o, o_single, inner_at(i), kv_outer, skip_pad, pad_id, &att, &ful);
+            const unsigned am = __ballot_sync(0xffffffffu, att), fm = __ballot_sync(0xffffffffu, ful);
+            if (!up_done && am) { up = gi * kGroup + (31 - __clz(am)) + 1; up_done = true; }
+            if (!upf_done && fm) { upf = gi * kGroup + (31 - __clz(fm)) + 1; upf_done = true; }
+          }
+        }
+        // host fix-ups, mask_creator.py:317-333
+        if (lo == n) lo = up;
+        if (lof == n) lof = kv_outer ? up : lo;
+        if (upf < lof) upf = lof;
+      } else {
+        lo = up = lof = upf = 0;
+      }
+      if (lane == 0) {
+        const long long idx = (long long)b * so.n_blocks + ob;
+        for (int m2 = m; m2 < a.n_masks; ++m2) {
+          if (m2 != m && a.masks[m2].same_as != m) continue;
+          a.masks[m2].lower[idx] = lo;
+          a.masks[m2].upper[idx] = up;
+          a.masks[m2].lower_full[idx] = lof;
+          a.masks[m2].upper_full[idx] = upf;
+        }
+      }
+    }
+  }
+  if (!all_local) cluster.sync();      // no CTA leaves while another may still read its summaries
+}
+
+constexpr size_t kClusterSmemLimit = 200 * 1024;
+constexpr size_t kClusterRowCopyLimit = 96 * 1024;     // beyond this the scans read the other CTAs' shared memory
+
+// KVAX_B200_EUNSUPPORTED when the row's summaries do not fit in shared memory (the caller then takes the
+// two-launch path); KVAX_B200_OK after a successful launch.
+int mask_build_clusters(const kvax_b200_mask_params* p, kvax_b200_stream_t stream) {
+  ClusterArgs a{};
+  a.batch = p->batch;
+  a.skip_pad = p->skip_pad_tokens ? 1 : 0;
+  a.n_masks = p->n_masks;
+  int max_blocks = 1;
+  auto find_set = [&](const int32_t* pos, const int32_t* seg, int len, int block, int pos_fill, int pad_id) {
+    for (int i = 0; i < a.n_sets; ++i) {
+      const SetDesc& sd = a.sets[i];
+      if (sd.pos == pos && sd.seg == seg && sd.len == len && sd.block == block && sd.pos_fill == pos_fill && sd.pad_id == pad_id) return i;
+    }
+    SetDesc& sd = a.sets[a.n_sets];
+    sd = SetDesc{pos, seg, len, block, cdiv(len, block), pos_fill, pad_id, 0, 0, -1};
+    if (sd.n_blocks > max_blocks) max_blocks = sd.n_blocks;
+    return a.n_sets++;
+  };
+  for (int m = 0; m < p->n_masks; ++m) {
+    const kvax_b200_mask_desc& d = p->masks[m];
+    const int pad_id = cdiv(p->kv_len, d.kv_block) * d.kv_block + 1;                 // :248
+    const int qs = find_set(p->q_positions, p->q_segment_ids, p->q_len, d.q_block, -1, pad_id);
+    const int ks = find_set(p->kv_positions, p->kv_segment_ids, p->kv_len, d.kv_block, INT_MAX, pad_id);
+    ClusterMask& mk = a.masks[m];
+    mk = ClusterMask{d.lower, d.upper, d.lower_full, d.upper_full, d.kv_outer ? ks : qs, d.kv_outer ? qs : ks, d.kv_outer ? 1 : 0, -1};
+    for (int e = 0; e < m; ++e)
+      if (a.masks[e].same_as < 0 && a.masks[e].outer_set == mk.outer_set && a.masks[e].inner_set == mk.inner_set &&
+          a.masks[e].kv_outer == mk.kv_outer) { mk.same_as = e; break; }
+  }
+  // CTAs per row: enough that a CTA summarises about one group of blocks per set, at most the portable cluster size
+  int cluster = 1;
+  while (cluster < 8 && cluster * kGroup < max_blocks) cluster *= 2;
+  a.cluster = cluster;
+  size_t off = 0;
+  for (int i = 0; i < a.n_sets; ++i) {
+    SetDesc& sd = a.sets[i];
+    const int per = ((cdiv(sd.n_blocks, cluster) + kGroup - 1) / kGroup) * kGroup;
+    sd.per = per;
+    sd.smem_off = int(off);
+    off += size_t(per) + size_t(per / kGroup);
+  }
+  if (off * sizeof(int4) > kClusterSmemLimit || (long long)p->batch * cluster > INT_MAX) return KVAX_B200_EUNSUPPORTED;
+  for (int i = 0; i < a.n_sets; ++i) {                  // private copies of the whole row, as long as they fit
+    SetDesc& sd = a.sets[i];
+    const size_t need = size_t(cluster) * sd.per + size_t(cluster) * sd.per / kGroup;
+    if ((off + need) * sizeof(int4) <= kClusterRowCopyLimit) {
+      sd.row_off = int(off);
+      off += need;
+    }
+  }
+  const size_t smem = off * sizeof(int4);
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(mask_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    return KVAX_B200_ELAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(p->batch) * cluster, 1, 1);
+  cfg.blockDim = dim3(kClusterThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = unsigned(cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, mask_cluster_kernel, a) == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+
 }  // namespace
 
 extern "C" size_t kvax_b200_mask_workspace_bytes(const kvax_b200_mask_params* p) {
@@ -179,10 +543,23 @@ extern "C" size_t kvax_b200_mask_workspace_bytes(const kvax_b200_mask_params* p)
   return total;
 }
 
-extern "C" int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
-                                    kvax_b200_stream_t stream) {
+namespace {
+
+int check_mask_params(const kvax_b200_mask_params* p) {
   if (!p || !p->q_positions || !p->q_segment_ids || !p->kv_positions || !p->kv_segment_ids) return KVAX_B200_EINVAL;
   if (p->batch <= 0 || p->q_len <= 0 || p->kv_len <= 0 || p->n_masks < 1 || p->n_masks > 3) return KVAX_B200_EINVAL;
+  for (int m = 0; m < p->n_masks; ++m) {
+    const kvax_b200_mask_desc& d = p->masks[m];
+    if (d.q_block <= 0 || d.kv_block <= 0) return KVAX_B200_EINVAL;
+    if (!d.lower || !d.upper || !d.lower_full || !d.upper_full) return KVAX_B200_EINVAL;
+    if ((long long)cdiv(p->kv_len, d.kv_block) * d.kv_block + 1 > INT_MAX) return KVAX_B200_EUNSUPPORTED;
+  }
+  return KVAX_B200_OK;
+}
+
+// Two launches through a summary area in global memory (the caller's workspace or the built-in scratch).
+int mask_build_two_launches(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
+                            kvax_b200_stream_t stream) {
   const size_t need = kvax_b200_mask_workspace_bytes(p);
   if (need == 0) return KVAX_B200_EINVAL;
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
@@ -224,6 +601,19 @@ extern "C" int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* worksp
   return KVAX_B200_OK;
 }
 
+}  // namespace
+
+extern "C" int kvax_b200_mask_build(const kvax_b200_mask_params* p, void* workspace, size_t workspace_bytes,
+                                    kvax_b200_stream_t stream) {
+  int rc = check_mask_params(p);
+  if (rc) return rc;
+  const size_t need = kvax_b200_mask_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
+  rc = mask_build_clusters(p, stream);
+  if (rc != KVAX_B200_EUNSUPPORTED) return rc;          // built, or a real error
+  return mask_build_two_launches(p, workspace, workspace_bytes, stream);
+}
+
 // ---------------------------------------------------------------------------------------
 // Variant with built-in scratch memory, for callers that cannot provide a workspace.
 // ---------------------------------------------------------------------------------------
@@ -257,5 +647,5 @@ extern "C" int kvax_b200_mask_build_static(const kvax_b200_mask_params* p, kvax_
     if (cudaGetSymbolAddress(&ptr, g_mask_scratch) != cudaSuccess || !ptr) return KVAX_B200_ENODEVICE;
     __atomic_store_n(&g_scratch_addr[dev], ptr, __ATOMIC_RELEASE);
   }
-  return kvax_b200_mask_build(p, ptr, kStaticScratchBytes, stream);
+  return mask_build_two_launches(p, ptr, kStaticScratchBytes, stream);
 }

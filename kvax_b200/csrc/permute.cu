@@ -68,3 +68,48 @@ extern "C" int kvax_b200_permute_tokens(const void* src, void* dst, int64_t batc
   }
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
+
+// ---------------------------------------------------------------------------------------
+// Head regrouping for the head-exchange schedule of context parallelism: one pass that
+// turns (B, S, cp * Hl, D) into the all-to-all send layout (cp, B, S, Hl, D) -- group r =
+// the heads rank r will own -- or back (`to_groups` = 0: (cp, B, S, Hl, D) -> (B, S, cp * Hl, D)).
+// Pure data movement, 16-byte vectors; `head_bytes` = D * element size (a multiple of 16).
+// ---------------------------------------------------------------------------------------
+namespace {
+
+__global__ void __launch_bounds__(256) regroup_heads_kernel(const int4* __restrict__ src, int4* __restrict__ dst,
+                                                           long long tokens, int cp, int hl, int head_vecs, int to_groups) {
+  // token-major view: grouped[r][t][h][v], flat[t][r][h][v]
+  const long long group_vecs = tokens * hl * head_vecs;      // vectors per group
+  const long long total = group_vecs * cp;
+  const int per_tok = hl * head_vecs;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    // i indexes the grouped layout
+    const long long r = i / group_vecs;
+    const long long rem = i - r * group_vecs;
+    const long long t = rem / per_tok;
+    const long long within = rem - t * per_tok;
+    const long long flat = (t * cp + r) * per_tok + within;
+    if (to_groups) dst[i] = __ldg(src + flat);
+    else dst[flat] = __ldg(src + i);
+  }
+}
+
+}  // namespace
+
+extern "C" int kvax_b200_regroup_heads(const void* src, void* dst, int64_t tokens, int32_t cp, int32_t heads_per_group,
+                                       int64_t head_bytes, int32_t to_groups, kvax_b200_stream_t stream) {
+  if (!src || !dst || src == dst || tokens <= 0 || cp <= 0 || heads_per_group <= 0 || head_bytes <= 0) return KVAX_B200_EINVAL;
+  if ((head_bytes & 15) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return KVAX_B200_EUNSUPPORTED;
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long total = tokens * cp * heads_per_group * (head_bytes / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
+  regroup_heads_kernel<<<int(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int4*>(src), static_cast<int4*>(dst), tokens, cp, heads_per_group, int(head_bytes / 16), to_groups);
+  return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}

@@ -32,6 +32,7 @@ from __future__ import annotations
 import math
 
 import torch
+import torch.distributed
 
 from kvax_b200 import _lib
 from kvax_b200._status import check_last_status, status_word
@@ -296,6 +297,110 @@ def _gather_tokens(x: torch.Tensor, cp: int, group, permuted: bool, permute_fn=N
     return _gather_kv(x.unsqueeze(-1).unsqueeze(-1), cp, group, permuted, permute_fn)[:, :, 0, 0].contiguous()
 
 
+def _regroup_heads(x: torch.Tensor, cp: int, to_groups: bool) -> torch.Tensor:
+    """(B, S, cp * Hl, D) -> (cp, B, S, Hl, D) (group r = the heads rank r owns) or back, in one pass.
+    On CUDA tensors this is the regroup kernel of the library; on CPU tensors (the gloo tests of the
+    exchange logic) the same index map with torch ops."""
+    if to_groups:
+        B, S, H, D = x.shape
+        hl = H // cp
+        if not x.is_cuda:
+            return x.reshape(B, S, cp, hl, D).permute(2, 0, 1, 3, 4).contiguous()
+        x = x.contiguous()
+        out = torch.empty((cp, B, S, hl, D), dtype=x.dtype, device=x.device)
+    else:
+        _, B, S, hl, D = x.shape
+        if not x.is_cuda:
+            return x.permute(1, 2, 0, 3, 4).reshape(B, S, cp * hl, D)
+        x = x.contiguous()
+        out = torch.empty((B, S, cp * hl, D), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().kvax_b200_regroup_heads(x.data_ptr(), out.data_ptr(), B * S, cp, hl, D * x.element_size(),
+                                                 int(to_groups), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(rc, "kvax_b200_regroup_heads")
+    return out
+
+
+def _chunk_of(rank: int, half: int, cp: int, permuted: bool) -> int:
+    """Index (in units of half a local sequence) at which half `half` (0 / 1) of rank `rank`'s local tokens sits in
+    the natural order: with the load-balancing permutation rank r holds chunks r and 2 CP - 1 - r."""
+    if not permuted:
+        return 2 * rank + half
+    return rank if half == 0 else 2 * cp - 1 - rank
+
+
+def _exchange_seq_to_heads(tensors, cp: int, rank: int, group, permuted: bool):
+    """Head exchange, sequence sharding -> head sharding, for several (1, S_loc, H, D) tensors at once.
+    One regroup pass per tensor builds the send layout; every peer's two half-sequences are then received
+    straight into their place in natural token order (no gather buffer, no un-permutation pass), all sends
+    and receives of all tensors in one NCCL group."""
+    import torch.distributed as dist
+    outs, ops, local_copies = [], [], []
+    ranks = dist.get_process_group_ranks(group) if group is not None else list(range(cp))
+    for x in tensors:
+        B, Sl, H, D = x.shape
+        assert B == 1 and Sl % 2 == 0
+        hl, half = H // cp, Sl // 2
+        send = _regroup_heads(x, cp, True)                       # (cp, 1, Sl, hl, D)
+        nat = torch.empty((1, cp * Sl, hl, D), dtype=x.dtype, device=x.device)
+        outs.append(nat)
+        for r in range(cp):
+            for h in range(2):
+                c = _chunk_of(r, h, cp, permuted)
+                dst = nat[0, c * half:(c + 1) * half]           # contiguous: tokens of rank r, half h, my heads
+                src = send[r, 0, h * half:(h + 1) * half]       # contiguous: my tokens, half h, heads of rank r
+                if r == rank:
+                    local_copies.append((nat[0, _chunk_of(rank, h, cp, permuted) * half:(_chunk_of(rank, h, cp, permuted) + 1) * half], src))
+                else:
+                    ops.append(dist.P2POp(dist.isend, src, ranks[r], group))
+                    ops.append(dist.P2POp(dist.irecv, dst, ranks[r], group))
+    for dst, src in local_copies:
+        dst.copy_(src)
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return outs
+
+
+def _exchange_heads_to_seq(tensors, cp: int, rank: int, group, permuted: bool):
+    """Inverse exchange for several (1, S, Hl, D) natural-order tensors: every peer's two half-sequences are
+    sent straight out of the natural-order tensor, the received head groups are interleaved by one regroup
+    pass.  Returns (1, S_loc, cp * Hl, D) tensors."""
+    import torch.distributed as dist
+    recvs, ops, local_copies = [], [], []
+    ranks = dist.get_process_group_ranks(group) if group is not None else list(range(cp))
+    for y in tensors:
+        B, S, hl, D = y.shape
+        assert B == 1
+        y = y.contiguous()
+        Sl = S // cp
+        half = Sl // 2
+        recv = torch.empty((cp, 1, Sl, hl, D), dtype=y.dtype, device=y.device)
+        recvs.append(recv)
+        for r in range(cp):
+            for h in range(2):
+                c = _chunk_of(r, h, cp, permuted)
+                src = y[0, c * half:(c + 1) * half]             # tokens of rank r, half h, my heads
+                dst = recv[r, 0, h * half:(h + 1) * half]       # my tokens, half h, heads of rank r
+                if r == rank:
+                    local_copies.append((dst, y[0, _chunk_of(rank, h, cp, permuted) * half:(_chunk_of(rank, h, cp, permuted) + 1) * half]))
+                else:
+                    ops.append(dist.P2POp(dist.isend, src, ranks[r], group))
+                    ops.append(dist.P2POp(dist.irecv, dst, ranks[r], group))
+    for dst, src in local_copies:
+        dst.copy_(src)
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return [_regroup_heads(r_, cp, False) for r_ in recvs]
+
+
+def _fast_exchange_ok(x: torch.Tensor) -> bool:
+    """The zero-copy exchange places half-sequences as contiguous slices, which needs batch 1 (the shape of the
+    context-parallel workloads); other shapes take the copy-based all-to-all."""
+    return x.shape[0] == 1 and x.shape[1] % 2 == 0 and (x.shape[3] * x.element_size()) % 16 == 0
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, masks, scale, fwd_params, bwd_params,
@@ -348,9 +453,14 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
                 sequential, permuted, cp, group):
         from kvax_b200.ops.mask_creator import build_masks
 
-        q_h = _seq_to_heads(query, cp, group, permuted)
-        k_h = _seq_to_heads(key, cp, group, permuted)
-        v_h = _seq_to_heads(value, cp, group, permuted)
+        rank = torch.distributed.get_rank(group)
+        fast = _fast_exchange_ok(query) and _fast_exchange_ok(key) and _fast_exchange_ok(value)
+        if fast:
+            q_h, k_h, v_h = _exchange_seq_to_heads((query, key, value), cp, rank, group, permuted)
+        else:
+            q_h = _seq_to_heads(query, cp, group, permuted)
+            k_h = _seq_to_heads(key, cp, group, permuted)
+            v_h = _seq_to_heads(value, cp, group, permuted)
         q_pos_f = _gather_tokens(q_pos, cp, group, permuted)
         q_seg_f = _gather_tokens(q_seg, cp, group, permuted)
         specs = [(fwd_params.query_block_size, fwd_params.kv_block_size, False)]
@@ -364,7 +474,9 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         ctx.save_for_backward(q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = n_masks
-        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype)
+        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype, rank, fast)
+        if fast:
+            return _exchange_heads_to_seq((out_h,), cp, rank, group, permuted)[0]
         return _heads_to_seq(out_h, cp, group, permuted)
 
     @staticmethod
@@ -376,14 +488,20 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         if ctx.n_masks != 3:
             raise ValueError("Length of mask_tensors should be equal to two")
         masks = [AttentionMask.unflatten(flat[4 * i:4 * i + 4]) for i in range(3)]
-        scale, bwd_params, sequential, permuted, cp, group, kv_dtype = ctx.cfg
+        scale, bwd_params, sequential, permuted, cp, group, kv_dtype, rank, fast = ctx.cfg
         bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
         if q_h.shape[1] % bq or k_h.shape[1] % bk:
             raise AssertionError("sequence lengths must be divisible by the backward block sizes")
-        dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
+        if fast:
+            dout_h = _exchange_seq_to_heads((dout,), cp, rank, group, permuted)[0]
+        else:
+            dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
         dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
                                                  masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
         # every dK / dV element is complete on this rank: cast first, then exchange
+        if fast:
+            dq, dk, dv = _exchange_heads_to_seq((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), cp, rank, group, permuted)
+            return (dq, dk, dv) + (None,) * 12
         dq = _heads_to_seq(dq_h, cp, group, permuted)
         dk = _heads_to_seq(dk_h.to(kv_dtype), cp, group, permuted)
         dv = _heads_to_seq(dv_h.to(kv_dtype), cp, group, permuted)

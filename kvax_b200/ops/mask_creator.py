@@ -32,47 +32,62 @@ def _as_i32(x: torch.Tensor, name: str) -> torch.Tensor:
     return x.to(torch.int32).contiguous()
 
 
+class MaskPlan:
+    """One prepared call of kvax_b200_mask_build: argument struct, output arrays and workspace are set up once,
+    `launch()` only enqueues the kernel on the current stream (for callers that rebuild masks of the same shape
+    into the same arrays every step, and for timing the kernel without host overhead)."""
+
+    def __init__(self, query_positions, query_segment_ids, kv_positions, kv_segment_ids, block_specs, skip_pad_tokens=True):
+        qp = _as_i32(query_positions, "query_positions")
+        qs = _as_i32(query_segment_ids, "query_segment_ids")
+        kp = _as_i32(kv_positions, "kv_positions")
+        ks = _as_i32(kv_segment_ids, "kv_segment_ids")
+        B, Sq = qp.shape
+        Skv = kp.shape[1]
+        if qs.shape != (B, Sq) or kp.shape != (B, Skv) or ks.shape != (B, Skv):
+            raise AssertionError("positions / segment ids have inconsistent shapes")
+        self._keep = (qp, qs, kp, ks)
+        self._lib = _lib.load()
+        self.device = qp.device
+        p = self.params = _lib.MaskParams()
+        p.q_positions, p.q_segment_ids = qp.data_ptr(), qs.data_ptr()
+        p.kv_positions, p.kv_segment_ids = kp.data_ptr(), ks.data_ptr()
+        p.batch, p.q_len, p.kv_len = B, Sq, Skv
+        p.skip_pad_tokens = int(bool(skip_pad_tokens))
+        p.n_masks = len(block_specs)
+        for i, (bq, bk, kv_outer) in enumerate(block_specs):
+            d = p.masks[i]
+            d.q_block, d.kv_block, d.kv_outer = int(bq), int(bk), int(bool(kv_outer))
+        self.ws_bytes = self._lib.kvax_b200_mask_workspace_bytes(p)
+        if self.ws_bytes == 0:
+            raise _lib.KvaxB200Error("kvax_b200_mask_workspace_bytes rejected the arguments")
+        # one allocation holds the workspace and every output array (each output starts on a 256-byte boundary)
+        sizes = [(Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq for (bq, bk, kv_outer) in block_specs]
+        out_bytes = [((4 * B * n * 4 + 255) // 256) * 256 for n in sizes]
+        ws_aligned = ((self.ws_bytes + 255) // 256) * 256
+        self._blob = torch.empty(ws_aligned + sum(out_bytes), dtype=torch.uint8, device=qp.device)
+        outs, off = [], ws_aligned
+        for i, n in enumerate(sizes):
+            arrs = self._blob[off:off + 4 * B * n * 4].view(torch.int32).view(4, B, 1, n)
+            off += out_bytes[i]
+            d = p.masks[i]
+            d.lower, d.upper, d.lower_full, d.upper_full = (arrs[j].data_ptr() for j in range(4))
+            outs.append(arrs)
+        self.masks = tuple(AttentionMask(a[0], a[1], a[2], a[3]) for a in outs)
+
+    def launch(self) -> tuple[AttentionMask, ...]:
+        with torch.cuda.device(self.device):
+            rc = self._lib.kvax_b200_mask_build(self.params, self._blob.data_ptr(), self.ws_bytes,
+                                                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(rc, "kvax_b200_mask_build")
+        return self.masks
+
+
 def build_masks(query_positions, query_segment_ids, kv_positions, kv_segment_ids,
                 block_specs, skip_pad_tokens=True):
     """`block_specs`: up to three (query_block, kv_block, kv_outer) triples.  Returns one
     AttentionMask per triple.  This is the direct wrapper of kvax_b200_mask_build."""
-    qp = _as_i32(query_positions, "query_positions")
-    qs = _as_i32(query_segment_ids, "query_segment_ids")
-    kp = _as_i32(kv_positions, "kv_positions")
-    ks = _as_i32(kv_segment_ids, "kv_segment_ids")
-    B, Sq = qp.shape
-    Skv = kp.shape[1]
-    if qs.shape != (B, Sq) or kp.shape != (B, Skv) or ks.shape != (B, Skv):
-        raise AssertionError("positions / segment ids have inconsistent shapes")
-    lib = _lib.load()
-    p = _lib.MaskParams()
-    p.q_positions, p.q_segment_ids = qp.data_ptr(), qs.data_ptr()
-    p.kv_positions, p.kv_segment_ids = kp.data_ptr(), ks.data_ptr()
-    p.batch, p.q_len, p.kv_len = B, Sq, Skv
-    p.skip_pad_tokens = int(bool(skip_pad_tokens))
-    p.n_masks = len(block_specs)
-    for i, (bq, bk, kv_outer) in enumerate(block_specs):
-        d = p.masks[i]
-        d.q_block, d.kv_block, d.kv_outer = int(bq), int(bk), int(bool(kv_outer))
-    ws_bytes = lib.kvax_b200_mask_workspace_bytes(p)
-    if ws_bytes == 0:
-        raise _lib.KvaxB200Error("kvax_b200_mask_workspace_bytes rejected the arguments")
-    # one allocation holds the workspace and every output array (each output starts on a 256-byte boundary)
-    sizes = [(Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq for (bq, bk, kv_outer) in block_specs]
-    out_bytes = [((4 * B * n * 4 + 255) // 256) * 256 for n in sizes]
-    ws_aligned = ((ws_bytes + 255) // 256) * 256
-    blob = torch.empty(ws_aligned + sum(out_bytes), dtype=torch.uint8, device=qp.device)
-    outs, off = [], ws_aligned
-    for i, n in enumerate(sizes):
-        arrs = blob[off:off + 4 * B * n * 4].view(torch.int32).view(4, B, 1, n)
-        off += out_bytes[i]
-        d = p.masks[i]
-        d.lower, d.upper, d.lower_full, d.upper_full = (arrs[j].data_ptr() for j in range(4))
-        outs.append(arrs)
-    with torch.cuda.device(qp.device):
-        rc = lib.kvax_b200_mask_build(p, blob.data_ptr(), ws_bytes, torch.cuda.current_stream(qp.device).cuda_stream)
-    _lib.check(rc, "kvax_b200_mask_build")
-    return tuple(AttentionMask(a[0], a[1], a[2], a[3]) for a in outs)
+    return MaskPlan(query_positions, query_segment_ids, kv_positions, kv_segment_ids, block_specs, skip_pad_tokens).launch()
 
 
 def create_attention_mask(

@@ -14,8 +14,8 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from kvax_b200.ops.flash_attention import (_gather_kv, _gather_tokens, _heads_to_seq, _scatter_dkv, _seq_to_heads,  # noqa: E402
-                                            context_offsets)
+from kvax_b200.ops.flash_attention import (_exchange_heads_to_seq, _exchange_seq_to_heads, _gather_kv,  # noqa: E402
+                                            _gather_tokens, _heads_to_seq, _scatter_dkv, _seq_to_heads, context_offsets)
 from kvax_b200.utils.sharding import Mesh  # noqa: E402
 from oracle import permutation_oracle as po  # noqa: E402
 
@@ -59,6 +59,15 @@ def main():
             assert torch.equal(heads, fullh[:, :, 2 * rank:2 * rank + 2]), f"seq->heads mismatch B={B} permuted={permuted}"
             back = _heads_to_seq(heads, world, None, permuted, permute_fn=oracle_permute)
             assert torch.equal(back, mineh), f"heads->seq mismatch B={B} permuted={permuted}"
+            if B == 1:
+                # the zero-copy exchange (half-sequences received straight into natural order, several tensors per
+                # group of sends / receives) must give the same tensors as the copy-based all-to-all
+                other = torch.randn(B, loc, world, D, generator=torch.Generator().manual_seed(13 + rank))
+                fast, fast2 = _exchange_seq_to_heads((mineh, other), world, rank, None, permuted)
+                assert torch.equal(fast, heads), f"zero-copy seq->heads mismatch permuted={permuted}"
+                assert torch.equal(fast2, _seq_to_heads(other, world, None, permuted, permute_fn=oracle_permute))
+                back1, back2 = _exchange_heads_to_seq((fast, fast2), world, rank, None, permuted)
+                assert torch.equal(back1, mineh) and torch.equal(back2, other), f"zero-copy heads->seq mismatch permuted={permuted}"
             tok = torch.arange(B * S, dtype=torch.int32).view(B, S)
             tokg = (oracle_permute(tok.view(B, S, 1, 1), world, False).view(B, S) if permuted else tok)
             gathered = _gather_tokens(tokg[:, rank * loc:(rank + 1) * loc].contiguous(), world, None, permuted, permute_fn=oracle_permute)
@@ -82,6 +91,9 @@ def main():
             heads = _seq_to_heads(mine, cp, group, True, permute_fn=oracle_permute)
             assert torch.equal(heads, full[:, :, 2 * crank:2 * crank + 2])
             assert torch.equal(_heads_to_seq(heads, cp, group, True, permute_fn=oracle_permute), mine)
+            (fast,) = _exchange_seq_to_heads((mine,), cp, crank, group, True)
+            assert torch.equal(fast, heads)
+            assert torch.equal(_exchange_heads_to_seq((fast,), cp, crank, group, True)[0], mine)
             out = _scatter_dkv((crank + 1.0) * full, cp, group, True, torch.float32, permute_fn=oracle_permute)
             assert torch.allclose(out, 3.0 * mine)
     dist.barrier()

@@ -72,3 +72,39 @@ def test_public_api_shapes_and_errors():
     assert len(one) == 1 and len(three) == 3
     assert tuple(one[0].lower_bounds.shape) == (cfg.batch, 1, 4)
     assert one[0].lower_bounds.dtype == torch.int32
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_mask_kernel_on_unordered_segments_and_positions(seed):
+    """Nothing in the builder may rely on sorted inputs: random segment ids (with PAD sprinkled in) and random
+    positions, several block sizes per call.  The group summaries of the cluster path then rule out little and
+    every scan path (first / last hit in any group) is exercised against the oracle."""
+    rng = np.random.default_rng(seed)
+    B, S = 3, 4096 + 64 * seed
+    seg = rng.integers(0, 6, size=(B, S)).astype(np.int32)
+    seg[rng.random((B, S)) < 0.2] = -1
+    seg[:, 1000:1400] = -1                      # all-PAD blocks in the middle
+    seg[1, 2048:2304] = 3                       # single-segment blocks
+    pos = rng.integers(0, 5000, size=(B, S)).astype(np.int32)
+    pos[1, 2048:2304] = np.arange(256)
+    for skip in (True, False):
+        fwd, bwd = (128, 64), (64, 32)
+        masks = _build(pos, seg, pos, seg, fwd, bwd, skip)
+        ref = mo.create_attention_mask(pos, seg, pos, seg, fwd, bwd, calc_bwd_mask=True, skip_pad_tokens=skip)
+        for m, rm in zip(masks, ref):
+            for t, a in zip(m.flatten(), rm):
+                np.testing.assert_array_equal(t.cpu().numpy(), a)
+
+
+def test_mask_kernel_many_blocks_per_row():
+    """2048 blocks per row (128k tokens at block 64): more than 32 groups of 32 blocks, 256 blocks per CTA of
+    the cluster."""
+    cfg = gen.CONFIGS["c5_cp_128k"]
+    inp = gen.make_inputs(cfg, with_tensors=False, seed=3)
+    p, s = inp["positions"], inp["segment_ids"]
+    fwd, bwd = (64, 64), (64, 64)
+    masks = _build(p, s, p, s, fwd, bwd, True)
+    ref = mo.create_attention_mask(p, s, p, s, fwd, bwd, calc_bwd_mask=True, skip_pad_tokens=True)
+    for m, rm in zip(masks, ref):
+        for t, a in zip(m.flatten(), rm):
+            np.testing.assert_array_equal(t.cpu().numpy(), a)
