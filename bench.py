@@ -192,6 +192,43 @@ def cpu_dense_sample(cfg, inp, seconds_target=12.0):
     return flops / sec / 1e12, sample, sec, cores
 
 
+def mask_builder_numbers(q_pos, q_seg, kv_pos, kv_seg, dev, peaks, public_call_ms=None):
+    """The block-mask builder on the step's own arrays and on two larger synthetic layouts.
+    `at_workload_us`: the public call (host work + launch); `at_workload_kernel_us`: the kernel alone through a
+    prepared call.  The benchmark configurations are <= 2 MiB of input, i.e. latency bound, so bandwidth is
+    measured on (B 2048, S 4096) and (B 64, S 131072): documents of 1000 tokens, 128-token blocks, three masks;
+    algorithmic bytes = 16 B S (four int32 inputs read once) + 48 B S / 128 (twelve int32 outputs)."""
+    from kvax_b200.ops.mask_creator import MaskPlan
+    spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
+    plan = MaskPlan(q_pos, q_seg, kv_pos, kv_seg, spec3, True)
+    plan.launch()
+    info = {"at_workload_us": None if public_call_ms is None else public_call_ms * 1e3,
+            "at_workload_kernel_us": cuda_time(plan.launch, 50) * 1e3}
+    for (mb, ms_) in ((2048, 4096), (64, 131072)):
+        mp = (torch.arange(ms_, device=dev, dtype=torch.int32) % 1000).repeat(mb, 1)
+        msg = (torch.arange(ms_, device=dev, dtype=torch.int32) // 1000).repeat(mb, 1)
+        plan = MaskPlan(mp, msg, mp, msg, spec3, True)
+        plan.launch()
+        t_ms = cuda_time(plan.launch, 20)
+        alg = 16.0 * mb * ms_ + 48.0 * mb * ms_ / TILE
+        info[f"B{mb}_S{ms_}"] = {"ms": t_ms, "algorithmic_GBps": alg / (t_ms * 1e-3) / 1e9,
+                                 "frac_of_hbm": alg / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        del mp, msg, plan
+    return info
+
+
+def run_mask_only(args):
+    """`--mask-only`: just the mask builder numbers of `mask_builder_numbers` on the single-GPU workload
+    (72 launches of the builder before the two of the largest layout: a fixed point for a profiler)."""
+    name = args.workload or "c4_docmask_32k"
+    inp = gen.make_inputs(gen.CONFIGS[name], seed=0, with_tensors=False)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pos, seg = torch.from_numpy(inp["positions"]).to(dev), torch.from_numpy(inp["segment_ids"]).to(dev)
+    info = mask_builder_numbers(pos, seg, pos, seg, dev, measured_peaks())
+    print(json.dumps({"metric": "block-mask builder", "config": {"workload": name}, "mask_builder": info}), flush=True)
+
+
 def same_gpu_reference(q, k, v, do, pos, seg, scale, flops_fwd):
     """Times kvax's unmodified Triton kernels (host functions included) on this GPU on the step's own
     tensors: oracle/triton_reference.py, H100 launch setting of the reference (forward 128 x 128,
@@ -277,6 +314,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kvax_b200", choices=["kvax_b200", "reference"])
     ap.add_argument("--workload", default=None, help="override the configuration (c2_llama8b_8k, c3_dense_causal_16k, ...)")
+    ap.add_argument("--mask-only", action="store_true", help="only measure the block-mask builder (one GPU)")
     ap.add_argument("--no-other-schedule", action="store_true",
                     help="with --gpus N > 1: do not also time the all-gather schedule")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -286,6 +324,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.mask_only:
+        return run_mask_only(args)
 
     import kvax_b200 as kv
     from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status
@@ -515,25 +555,7 @@ def main():
         #      configurations are <= 2 MiB, i.e. launch bound) -----------------------------
         mask_info = None
         if cp == 1:
-            from kvax_b200.ops.mask_creator import MaskPlan
-            spec3 = [(TILE, TILE, False), (TILE, TILE, False), (TILE, TILE, True)]
-            # `at_workload_us`: the public call (host work + launch) on the step's own arrays; `kernel_us`: the kernel
-            # alone through a prepared call.  The benchmark configurations are <= 2 MiB of input, i.e. latency bound;
-            # bandwidth is measured on two larger synthetic layouts.
-            plan = MaskPlan(q_pos, q_seg, kv_pos, kv_seg, spec3, True)
-            plan.launch()
-            mask_info = {"at_workload_us": parts.get("mask_build_ms", 0.0) * 1e3,
-                         "at_workload_kernel_us": cuda_time(plan.launch, 50) * 1e3}
-            for (mb, ms_) in ((2048, 4096), (64, 131072)):
-                mp = (torch.arange(ms_, device=dev, dtype=torch.int32) % 1000).repeat(mb, 1)
-                msg = (torch.arange(ms_, device=dev, dtype=torch.int32) // 1000).repeat(mb, 1)
-                plan = MaskPlan(mp, msg, mp, msg, spec3, True)
-                plan.launch()
-                t_ms = cuda_time(plan.launch, 20)
-                alg = 16.0 * mb * ms_ + 48.0 * mb * ms_ / TILE
-                mask_info[f"B{mb}_S{ms_}"] = {"ms": t_ms, "algorithmic_GBps": alg / (t_ms * 1e-3) / 1e9,
-                                              "frac_of_hbm": alg / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-                del mp, msg, plan
+            mask_info = mask_builder_numbers(q_pos, q_seg, kv_pos, kv_seg, dev, peaks, parts.get("mask_build_ms"))
 
         # ---- end to end: pinned host buffers in, results back out, every step ----------
         e2e = None

@@ -262,7 +262,127 @@ __device__ __forceinline__ void block_tests(const int4& o, bool o_single, const 
   *full = both_single && pos_all && att;
 }
 
-__global__ void __launch_bounds__(kClusterThreads) mask_cluster_kernel(const ClusterArgs a) {
+
+// Where the summaries of a row's inner blocks are read from: the CTA's private copy of the whole row, or the
+// shared memory of the CTAs of the cluster that computed them.
+struct LocalReader {
+  const int4* row;         // block summaries of the whole row, then the group summaries
+  int total;               // block summaries in the copy (cluster * per)
+  __device__ __forceinline__ int4 inner(int i) const { return row[i]; }
+  __device__ __forceinline__ int4 group(int g) const { return row[total + g]; }
+};
+struct RemoteReader {
+  cg::cluster_group cluster;
+  int4* base;              // this set's area in every CTA: `per` block summaries, then per / kGroup group summaries
+  int per;
+  __device__ __forceinline__ int4 inner(int i) const {
+    const int rank = i / per;
+    return *(cluster.map_shared_rank(base, rank) + (i - rank * per));
+  }
+  __device__ __forceinline__ int4 group(int g) const {
+    const int gper = per / kGroup, rank = g / gper;
+    return *(cluster.map_shared_rank(base, rank) + per + (g - rank * gper));
+  }
+};
+
+// The four bounds of one outer block (whole warp), before the fix-ups: lower / upper over `attend`, lower_full /
+// upper_full over `full`, `n` / 0 when nothing is found.  Group summaries rule out groups of 32 inner blocks: a group
+// passes the interval tests whenever one of its members does (the PAD test is left to the members, it is not monotone
+// under min / max).  Only the first and the last group with a hit are looked at block by block, plus -- rarely -- the
+// groups between them when the `full` range does not show in those two.
+template <class Reader>
+__device__ __forceinline__ void find_bounds(const Reader& rd, const int4 o, const bool o_single, const int n, const int n_groups,
+                                            const bool kv_outer, const bool skip_pad, const int pad_id, const int lane,
+                                            int& lo, int& up, int& lof, int& upf) {
+  lo = n; up = 0; lof = n; upf = 0;
+  auto candidates = [&](int g0) -> unsigned {
+    const int g = g0 + lane;
+    bool cand = false, ful;
+    if (g < n_groups) block_tests(o, o_single, rd.group(g), kv_outer, false, pad_id, &cand, &ful);
+    return __ballot_sync(0xffffffffu, cand);
+  };
+  auto members = [&](int gi, unsigned& am, unsigned& fm) {
+    const int i = gi * kGroup + lane;
+    bool att = false, ful = false;
+    if (i < n) block_tests(o, o_single, rd.inner(i), kv_outer, skip_pad, pad_id, &att, &ful);
+    am = __ballot_sync(0xffffffffu, att);
+    fm = __ballot_sync(0xffffffffu, ful);
+  };
+  if (n_groups <= 32) {
+    const unsigned cand = candidates(0);
+    unsigned am = 0, fm = 0;
+    int g_first = -1;
+    for (unsigned rest = cand; rest; rest &= rest - 1) {            // ascending to the first group with a hit
+      const int gi = __ffs(rest) - 1;
+      members(gi, am, fm);
+      if (am) { g_first = gi; break; }
+    }
+    if (g_first < 0) return;
+    const unsigned am_f = am, fm_f = fm;
+    lo = g_first * kGroup + __ffs(am_f) - 1;
+    int g_last = g_first;
+    unsigned am_l = am_f, fm_l = fm_f;
+    for (unsigned high = cand & ~((2u << g_first) - 1u); high;) {   // descending to the last group with a hit
+      const int gi = 31 - __clz(high);
+      high &= ~(1u << gi);
+      members(gi, am, fm);
+      if (am) { g_last = gi; am_l = am; fm_l = fm; break; }
+    }
+    up = g_last * kGroup + (31 - __clz(am_l)) + 1;
+    if (!o_single) return;                                          // `full` needs a single-segment outer block
+    // `full` implies `attend`: the full range lies inside [g_first, g_last]
+    const unsigned mid = (g_last > g_first) ? (cand & ~((2u << g_first) - 1u) & ((1u << g_last) - 1u)) : 0u;
+    int g_lof = -1;
+    if (fm_f) { lof = g_first * kGroup + __ffs(fm_f) - 1; g_lof = g_first; }
+    else {
+      for (unsigned rest = mid; rest; rest &= rest - 1) {
+        const int gi = __ffs(rest) - 1;
+        members(gi, am, fm);
+        if (fm) { lof = gi * kGroup + __ffs(fm) - 1; g_lof = gi; break; }
+      }
+      if (g_lof < 0 && g_last > g_first && fm_l) { lof = g_last * kGroup + __ffs(fm_l) - 1; g_lof = g_last; }
+    }
+    if (g_lof < 0) return;                                          // no full block at all
+    if (g_last > g_first && fm_l) { upf = g_last * kGroup + (31 - __clz(fm_l)) + 1; return; }
+    for (unsigned high = mid; high;) {                              // descending through the groups in between
+      const int gi = 31 - __clz(high);
+      high &= ~(1u << gi);
+      if (gi < g_lof) break;
+      members(gi, am, fm);
+      if (fm) { upf = gi * kGroup + (31 - __clz(fm)) + 1; return; }
+    }
+    upf = g_first * kGroup + (31 - __clz(fm_f)) + 1;                // then the hit is in the first group (g_lof == g_first)
+    return;
+  }
+  // rows with more than 1024 inner blocks: windows of 32 groups, ascending for the first hits, descending for the last
+  bool lo_done = false, lof_done = !o_single;
+  for (int g0 = 0; g0 < n_groups && !(lo_done && lof_done); g0 += 32) {
+    unsigned rest = candidates(g0);
+    while (rest && !(lo_done && lof_done)) {
+      const int gi = g0 + __ffs(rest) - 1;
+      rest &= rest - 1;
+      unsigned am, fm;
+      members(gi, am, fm);
+      if (!lo_done && am) { lo = gi * kGroup + __ffs(am) - 1; lo_done = true; }
+      if (!lof_done && fm) { lof = gi * kGroup + __ffs(fm) - 1; lof_done = true; }
+    }
+  }
+  bool up_done = !lo_done, upf_done = !(o_single && lof != n);
+  for (int g0 = ((n_groups - 1) / 32) * 32; g0 >= 0 && !(up_done && upf_done); g0 -= 32) {
+    unsigned rest = candidates(g0);
+    while (rest && !(up_done && upf_done)) {
+      const int bit = 31 - __clz(rest);
+      rest &= ~(1u << bit);
+      const int gi = g0 + bit;
+      unsigned am, fm;
+      members(gi, am, fm);
+      if (!up_done && am) { up = gi * kGroup + (31 - __clz(am)) + 1; up_done = true; }
+      if (!upf_done && fm) { upf = gi * kGroup + (31 - __clz(fm)) + 1; upf_done = true; }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kClusterThreads, 2) mask_cluster_kernel(const ClusterArgs a) {
   extern __shared__ int4 sm[];
   cg::cluster_group cluster = cg::this_cluster();
   const int c = int(cluster.block_rank());
@@ -366,91 +486,39 @@ __global__ void __launch_bounds__(kClusterThreads) mask_cluster_kernel(const Clu
     const SetDesc& so = a.sets[mk.outer_set];
     const SetDesc& si = a.sets[mk.inner_set];
     const int n = si.n_blocks, n_groups = (n + kGroup - 1) / kGroup;
-    const int groups_per_cta = si.per / kGroup;
     const bool kv_outer = mk.kv_outer != 0, skip_pad = a.skip_pad != 0;
     const int pad_id = so.pad_id;
     const int4* o_sum = sm + so.smem_off;
-    int4* in_base = sm + si.smem_off;
-    const int4* in_row = si.row_off >= 0 ? sm + si.row_off : nullptr;
-    const int in_total = a.cluster * si.per;
-    auto inner_at = [&](int i) -> int4 {                            // summary of inner block i, wherever it lives
-      if (in_row) return in_row[i];
-      const int rank = i / si.per;
-      return *(cluster.map_shared_rank(in_base, rank) + (i - rank * si.per));
-    };
-    auto group_at = [&](int g) -> int4 {
-      if (in_row) return in_row[in_total + g];
-      const int rank = g / groups_per_cta;
-      return *(cluster.map_shared_rank(in_base, rank) + si.per + (g - rank * groups_per_cta));
-    };
+    const LocalReader local{si.row_off >= 0 ? sm + si.row_off : nullptr, a.cluster * si.per};
+    const RemoteReader remote{cluster, sm + si.smem_off, si.per};
+    // results of mask m also go to the masks with the same geometry
+    int32_t* out[3][4];
+    int n_out = 0;
+    for (int m2 = m; m2 < a.n_masks; ++m2) {
+      if (m2 != m && a.masks[m2].same_as != m) continue;
+      out[n_out][0] = a.masks[m2].lower; out[n_out][1] = a.masks[m2].upper;
+      out[n_out][2] = a.masks[m2].lower_full; out[n_out][3] = a.masks[m2].upper_full;
+      ++n_out;
+    }
     for (int k = warp; k < so.per; k += kWarps) {
       const int ob = c * so.per + k;
       if (ob >= so.n_blocks) break;
       const int4 o = o_sum[k];
       const bool o_single = (o.x == o.y);
-      int lo = n, up = 0, lof = n, upf = 0;
-      const bool outer_all_pad = skip_pad && o_single && (o.x == pad_id);              // :69-76
+      int lo = 0, up = 0, lof = 0, upf = 0;
+      const bool outer_all_pad = skip_pad && o_single && (o.x == pad_id);              // :69-76: all four stay 0
       if (!outer_all_pad) {
-        // A group summary passes the interval tests whenever one of its members does (the PAD test is left to the
-        // members: it is not monotone under min / max).  `full` needs a single-segment outer block.
-        auto group_candidates = [&](int g0) -> unsigned {
-          const int g = g0 + lane;
-          bool cand = false;
-          if (g < n_groups) {
-            bool ful;
-            block_tests(o, o_single, group_at(g), kv_outer, false, pad_id, &cand, &ful);
-          }
-          return __ballot_sync(0xffffffffu, cand);
-        };
-        // ascending over the groups that can hold a hit: first `attend` -> lower, first `full` -> lower_full
-        const bool one_step = n_groups <= 32;                       // the usual case: the candidate mask is computed once
-        const unsigned cand0 = one_step ? group_candidates(0) : 0u;
-        bool lo_done = false, lof_done = !o_single;
-        for (int g0 = 0; g0 < n_groups && !(lo_done && lof_done); g0 += 32) {
-          unsigned rest = one_step ? cand0 : group_candidates(g0);
-          while (rest && !(lo_done && lof_done)) {
-            const int gi = g0 + __ffs(rest) - 1;
-            rest &= rest - 1;
-            const int i = gi * kGroup + lane;
-            bool att = false, ful = false;
-            if (i < n) block_tests(o, o_single, inner_at(i), kv_outer, skip_pad, pad_id, &att, &ful);
-            const unsigned am = __ballot_sync(0xffffffffu, att), fm = __ballot_sync(0xffffffffu, ful);
-            if (!lo_done && am) { lo = gi * kGroup + __ffs(am) - 1; lo_done = true; }
-            if (!lof_done && fm) { lof = gi * kGroup + __ffs(fm) - 1; lof_done = true; }
-          }
-        }
-        // descending: last `attend` -> upper, last `full` -> upper_full (none of either if the ascending pass found none)
-        bool up_done = !lo_done, upf_done = !(o_single && lof != n);
-        for (int g0 = ((n_groups - 1) / 32) * 32; g0 >= 0 && !(up_done && upf_done); g0 -= 32) {
-          unsigned rest = one_step ? cand0 : group_candidates(g0);
-          while (rest && !(up_done && upf_done)) {
-            const int bit = 31 - __clz(rest);
-            rest &= ~(1u << bit);
-            const int gi = g0 + bit;
-            const int i = gi * kGroup + lane;
-            bool att = false, ful = false;
-            if (i < n) block_tests(o, o_single, inner_at(i), kv_outer, skip_pad, pad_id, &att, &ful);
-            const unsigned am = __ballot_sync(0xffffffffu, att), fm = __ballot_sync(0xffffffffu, ful);
-            if (!up_done && am) { up = gi * kGroup + (31 - __clz(am)) + 1; up_done = true; }
-            if (!upf_done && fm) { upf = gi * kGroup + (31 - __clz(fm)) + 1; upf_done = true; }
-          }
-        }
+        if (local.row) find_bounds(local, o, o_single, n, n_groups, kv_outer, skip_pad, pad_id, lane, lo, up, lof, upf);
+        else find_bounds(remote, o, o_single, n, n_groups, kv_outer, skip_pad, pad_id, lane, lo, up, lof, upf);
         // host fix-ups, mask_creator.py:317-333
         if (lo == n) lo = up;
         if (lof == n) lof = kv_outer ? up : lo;
         if (upf < lof) upf = lof;
-      } else {
-        lo = up = lof = upf = 0;
       }
-      if (lane == 0) {
+      if (lane < 4) {
         const long long idx = (long long)b * so.n_blocks + ob;
-        for (int m2 = m; m2 < a.n_masks; ++m2) {
-          if (m2 != m && a.masks[m2].same_as != m) continue;
-          a.masks[m2].lower[idx] = lo;
-          a.masks[m2].upper[idx] = up;
-          a.masks[m2].lower_full[idx] = lof;
-          a.masks[m2].upper_full[idx] = upf;
-        }
+        const int val = lane == 0 ? lo : (lane == 1 ? up : (lane == 2 ? lof : upf));
+        for (int t = 0; t < n_out; ++t) out[t][lane][idx] = val;
       }
     }
   }
