@@ -42,9 +42,10 @@ constexpr int kKStages = 3, kVStages = 3;
 
 enum FwdBar {
   B_QFULL = 0,
-  B_KFULL0, B_KFULL1, B_KFULL2,              // a K stage is free once S_FULL of the entry that used it has completed
+  B_KFULL0, B_KFULL1, B_KFULL2, B_KEMPTY0, B_KEMPTY1, B_KEMPTY2,
   B_VFULL0, B_VFULL1, B_VFULL2, B_VEMPTY0, B_VEMPTY1, B_VEMPTY2,
   B_SFULL0, B_SFULL1, B_PFULL0, B_PFULL1,
+  B_ALLDONE,                                 // the last P V of the CTA (and with it every MMA) has completed: completes once
   B_LFULL, B_COUNT
 };
 
@@ -133,10 +134,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int st = it % kKStages, use = it / kKStages;
         const int u = int(e_next & ~kPartialBit);
         if (it + 1 < count) e_next = __ldg(list + it + 1);
-        if (use > 0) {      // the stage is free once QK(it - 3) has completed: that commit arrives on S_FULL
-          const int prev = it - kKStages;
-          ok = mbar_wait(&bars[B_SFULL0 + (prev & 1)], (prev >> 1) & 1, abort_flag, a.status, B_SFULL0 + (prev & 1));
-        }
+        if (use > 0) ok = mbar_wait(&bars[B_KEMPTY0 + st], (use - 1) & 1, abort_flag, a.status, B_KEMPTY0 + st);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars[B_KFULL0 + st], L::kTileBytes);
 #pragma unroll
@@ -189,7 +187,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const uint32_t off = ((kk >> 2) * L::kBoxBytes + (kk & 3) * 32) >> 4;   // 16 bf16 = 32 B inside a 128 B row
           umma_ss_lo(ts, q_lo + off, k_lo + off, idesc_s, kk > 0);
         }
-        umma_commit(&bars[B_SFULL0 + (it & 1)]);      // also tells the K producer that stage `st` is free
+        umma_commit(&bars[B_SFULL0 + (it & 1)]);
+        umma_commit(&bars[B_KEMPTY0 + st]);           // the K producer may refill the stage
       }
       __syncwarp();
     };
@@ -209,7 +208,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
           umma_ts_lo(tO + g * kTile, tp + kk * 8, v_lo + ((kk * 16 * 128) >> 4), idesc_o, (it > 1 || kk > 0) ? 1u : 0u);
-        umma_commit(&bars[B_VEMPTY0 + vs]);           // V stage free; P V(it) done (rescale, epilogue)
+        umma_commit(&bars[B_VEMPTY0 + vs]);           // V stage free; P V(it) done (rescale)
+        if (it + 1 == n) umma_commit(&bars[B_ALLDONE]);
       }
       __syncwarp();
       if (it + 2 < n) issue_qk(it + 2);   // reuses buffer g: issued after PV(it), which read P(it)
@@ -327,10 +327,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ---- epilogue: merge the two groups, normalise, store.  The (m, l) pairs are exchanged
     // through the (now idle) Q tile in shared memory; every thread then handles D/2 columns.
     float2* xl = reinterpret_cast<float2*>(sQ);              // [group][row]
-    if (ok) {                                               // all MMAs done: the last P V has completed
-      const int last = count - 1;
-      ok = mbar_wait(&bars[B_VEMPTY0 + last % kVStages], (last / kVStages) & 1, abort_flag, a.status, B_VEMPTY0 + last % kVStages);
-    }
+    // All MMAs done: the last P V has completed.  A barrier of its own that completes once: a group that finishes
+    // early would otherwise wait for a phase of a ring barrier that may lie more than one phase ahead, which a
+    // parity wait cannot tell from the phase before.
+    if (ok) ok = mbar_wait(&bars[B_ALLDONE], 0, abort_flag, a.status, B_ALLDONE);
     if (ok) {
       xl[wg * kTile + row] = make_float2(m, l);
       mbar_arrive(&bars[B_LFULL]);
