@@ -64,7 +64,40 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError("nvcc failed linking libkvax_b200.so")
     if verbose:
         print("\n".join(logs))
+    build_xla_ffi(verbose=verbose)
     return LIB
+
+
+def xla_ffi_include_dir() -> str | None:
+    """Directory that holds xla/ffi/api/ffi.h: XLA_FFI_INCLUDE_DIR, else jaxlib's copy, else None."""
+    d = os.environ.get("XLA_FFI_INCLUDE_DIR")
+    if d and os.path.exists(os.path.join(d, "xla", "ffi", "api", "ffi.h")):
+        return d
+    try:
+        import jax.ffi
+        d = jax.ffi.include_dir()
+        return d if os.path.exists(os.path.join(d, "xla", "ffi", "api", "ffi.h")) else None
+    except Exception:
+        return None
+
+
+def build_xla_ffi(verbose: bool = False) -> str | None:
+    """Compiles csrc/ffi_xla.cc (the XLA FFI handlers over the C ABI) into libkvax_b200_xla_ffi.so when the XLA FFI
+    headers are available; returns None (and says why when verbose) otherwise."""
+    inc = xla_ffi_include_dir()
+    if inc is None:
+        if verbose:
+            print("ffi_xla.cc not compiled: no xla/ffi/api/ffi.h (set XLA_FFI_INCLUDE_DIR or install jaxlib)")
+        return None
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    out = os.path.join(HERE, "libkvax_b200_xla_ffi.so")
+    cmd = [nvcc, "-std=c++17", "-O2", "-Xcompiler", "-fPIC", "-shared", "-I", inc, "-x", "cu", os.path.join(CSRC, "ffi_xla.cc"),
+           "-o", out, "-L", HERE, "-l:libkvax_b200.so", "-Xlinker", "-rpath=$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building libkvax_b200_xla_ffi.so")
+    return out
 
 
 if __name__ == "__main__":

@@ -145,9 +145,10 @@ struct TileList {
 };
 
 // Launch geometry shared by the attention kernels: a 1-D grid over (outer tile, head).
-// Outer tiles are taken in the longest-first order, in chunks of kRowChunk; inside a chunk
-// the heads are the slow index.  CTAs resident at the same time therefore belong to a few
-// heads and neighbouring outer tiles, so they stream the same inner tiles (served by L2),
+// Outer tiles are taken in the launch order built by schedule.cu (blocks of kRowChunk
+// neighbouring tiles, the blocks with the longest lists first), in chunks of kRowChunk; inside
+// a chunk the heads are the slow index.  CTAs resident at the same time therefore belong to a
+// few heads and neighbouring outer tiles, so they stream the same inner tiles (served by L2),
 // while long work items still start early in the launch.
 constexpr int kRowChunk = 32;
 __device__ __forceinline__ void decode_block(int linear, int n_rows, int n_heads, int* row_rank, int* head) {
