@@ -454,7 +454,7 @@ def main():
         ms_step = ms_total / K
 
         # ---- N > 1: numeric check against the one-GPU run of the same tensors, and the other schedule ---------------
-        cp_check, other_schedule = None, None
+        cp_check, other_schedule, cp_phases = None, None, None
         if cp > 1:
             def run_once():
                 for t_ in (q, k, v):
@@ -483,6 +483,13 @@ def main():
 
             if single is not None:
                 cp_check = {("head_exchange" if hx else "all_gather"): check(run_once())}
+            # where a step's time goes on this rank (CUDA events around the phases of the public call, rank 0)
+            from kvax_b200.ops import flash_attention as fa_mod
+            fa_mod.enable_phase_timing(True)
+            for _ in range(2):
+                step()
+            cp_phases = {k_: v_ / 2 for k_, v_ in fa_mod.phase_times_ms().items()}
+            fa_mod.enable_phase_timing(False)
             if hx and not args.no_other_schedule:     # the schedule the reference has: K/V all-gather, dK/dV reduce-scatter
                 kv.set_context_parallel_mode("all_gather")
                 for _ in range(2):
@@ -658,6 +665,7 @@ def main():
         line["same_workload_efficiency"] = same_1gpu["ms_per_step"] / (cp * ms_step)
     if cp > 1:
         line["cp_check"] = cp_check
+        line["cp_phases_ms_rank0"] = cp_phases
         if per_rank_tiles:
             mean = sum(per_rank_tiles) / len(per_rank_tiles)
             line["all_gather_tiles_per_rank"] = {"unmasked_tile_pairs": per_rank_tiles, "max_over_mean": max(per_rank_tiles) / mean,

@@ -181,8 +181,12 @@ typedef struct kvax_b200_attn_fwd_params {
   int32_t* status;                /* optional device int32, must be 0 on entry */
   /* 0 = everything; else bit set: 1 tile list, 2 attention kernel (see the backward). */
   int32_t stages;
-  int32_t reserved;
+  int32_t flags;                  /* KVAX_B200_FWD_*; 0: the library picks the kernel by sequence length */
 } kvax_b200_attn_fwd_params;
+
+/* Forward kernels: a CTA works on one 128-row query tile, or on two neighbouring ones that
+ * share every K / V tile brought on chip.  Same results either way. */
+enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2 };
 
 size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p);
 int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,

@@ -26,7 +26,8 @@ EXPORTS = (
     "kvax_b200_host_word_device_pointer",
 )
 
-BWD_TWO_KERNEL = 1          # kvax_b200_attn_bwd_params.flags
+BWD_TWO_KERNEL = 1
+FWD_ONE_TILE, FWD_TILE_PAIRS = 1, 2          # kvax_b200_attn_bwd_params.flags
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -58,7 +59,7 @@ class AttnShape(C.Structure):
 
 class AttnFwdParams(C.Structure):
     _fields_ = [("shape", AttnShape), ("q", vp), ("k", vp), ("v", vp), ("mask", BlockMask),
-                ("out", vp), ("lse", vp), ("status", vp), ("stages", i32), ("reserved", i32)]
+                ("out", vp), ("lse", vp), ("status", vp), ("stages", i32), ("flags", i32)]
 
 
 class AttnBwdParams(C.Structure):

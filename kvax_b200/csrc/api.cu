@@ -91,15 +91,17 @@ int mask_view(const kvax_b200_block_mask& m, bool kv_outer, int q_len, int kv_le
   return KVAX_B200_OK;
 }
 
-struct ListLayout { size_t tiles_off, counts_off, order_off, total; int n_outer, n_inner; };
+struct ListLayout { size_t tiles_off, counts_off, order_off, total; int n_outer, n_inner, batch; };
 
 ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base) {
   ListLayout l;
+  l.batch = batch;
   l.n_outer = cdiv(outer_len, kTile); l.n_inner = cdiv(inner_len, kTile);
   l.tiles_off = base;
   l.counts_off = l.tiles_off + align256(size_t(batch) * l.n_outer * l.n_inner * sizeof(uint32_t));
   l.order_off = l.counts_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
-  l.total = l.order_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
+  // launch order of the single tiles, then of the pairs of neighbouring tiles (the forward's work items)
+  l.total = l.order_off + align256(size_t(batch) * (l.n_outer + (l.n_outer + 1) / 2) * sizeof(int32_t));
   return l;
 }
 
@@ -119,13 +121,14 @@ void fill_schedule(ScheduleArgs* sa, const MaskView& mv, const TokenInfo& tok, c
   sa->tiles = reinterpret_cast<uint32_t*>(ws + ll.tiles_off);
   sa->counts = reinterpret_cast<int32_t*>(ws + ll.counts_off);
   sa->order = reinterpret_cast<int32_t*>(ws + ll.order_off);
+  sa->pair_order = sa->order + size_t(ll.batch) * ll.n_outer;
   sa->inner_summary = inner_summary;
   sa->n_outer_tiles = ll.n_outer; sa->n_inner_tiles = ll.n_inner;
   sa->outer_len = outer_len; sa->inner_len = inner_len;
 }
 
 void fill_list(TileList* l, const ScheduleArgs& sa) {
-  l->tiles = sa.tiles; l->counts = sa.counts; l->order = sa.order;
+  l->tiles = sa.tiles; l->counts = sa.counts; l->order = sa.order; l->pair_order = sa.pair_order;
   l->n_outer_tiles = sa.n_outer_tiles; l->n_inner_tiles = sa.n_inner_tiles;
 }
 
@@ -198,7 +201,12 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim;
-  return launch_attn_fwd(L, st);
+  // Two query tiles per CTA halve the K / V traffic and pay on long sequences; short ones have too few and too uneven
+  // CTAs that way (measured: 8k tokens 20 % slower, 16k dense 7 % faster, 32k document masks the same).
+  bool pairs = s.kv_len >= 16384;
+  if (p->flags & KVAX_B200_FWD_ONE_TILE) pairs = false;
+  if (p->flags & KVAX_B200_FWD_TILE_PAIRS) pairs = true;
+  return pairs ? launch_attn_fwd(L, st) : launch_attn_fwd_one(L, st);
 }
 
 namespace {

@@ -141,6 +141,7 @@ struct TileList {
   const uint32_t* tiles;   // (B, n_outer_tiles, n_inner_tiles)
   const int32_t* counts;   // (B, n_outer_tiles)
   const int32_t* order;    // (B * n_outer_tiles) launch order: row = b * n_outer_tiles + tile
+  const int32_t* pair_order;   // (B * ceil(n_outer_tiles / 2)) launch order of the pairs (2p, 2p+1): row of tile 2p
   int32_t n_outer_tiles, n_inner_tiles;
 };
 

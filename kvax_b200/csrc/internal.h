@@ -14,7 +14,8 @@ struct ScheduleArgs {
   TokenInfo tok;
   uint32_t* tiles;     // (B, n_outer_tiles, n_inner_tiles)
   int32_t* counts;     // (B, n_outer_tiles)
-  int32_t* order;      // (B * n_outer_tiles) rows sorted by list length, longest first
+  int32_t* order;      // (B * n_outer_tiles) launch order of the rows (blocks of neighbours, longest lists first)
+  int32_t* pair_order; // (B * ceil(n_outer_tiles / 2)) the same order for pairs (2p, 2p+1): row of the even tile
   const int4* inner_summary;  // (B, n_inner_tiles) {seg_min, seg_max, pos_min, pos_max}
   int32_t n_outer_tiles, n_inner_tiles;
   int32_t outer_len, inner_len;
@@ -40,7 +41,9 @@ struct FwdLaunch {
   FwdArgs args;
   int batch, head_dim;
 };
+// CTAs of two neighbouring query tiles that share their K / V tiles (attn_fwd.cu), or of one query tile (attn_fwd_one.cu).
 int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream);
+int launch_attn_fwd_one(const FwdLaunch& L, cudaStream_t stream);
 
 struct BwdArgs {
   TileList list;            // dQ kernel: one row per query tile; dK/dV kernel: per kv tile

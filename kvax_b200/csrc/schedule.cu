@@ -206,8 +206,10 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
 // of a batch: measured 22 GB of DRAM traffic per fused-backward launch on the 32k workload for 3 GB of algorithmic bytes.)
 // Counting sort of the blocks in one CTA; the order among blocks of equal key is not fixed.
 constexpr int kBins = 2048;
-__global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int32_t* order, int n_outer, int batch) {
-  __shared__ int hist[kBins];
+__global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int32_t* order, int32_t* pair_order, int n_outer,
+                                                     int batch) {
+  __shared__ int hist[kBins];        // rows per key, then the running start of the key's rows
+  __shared__ int hist2[kBins];       // the same in units of pairs of neighbouring rows
   const int blocks_per_row = (n_outer + kRowChunk - 1) / kRowChunk;
   const int n_blocks = blocks_per_row * batch;
   auto block_info = [&](int blk, int* first_row, int* rows) -> int {     // returns the key (mean list length, clamped)
@@ -219,18 +221,22 @@ __global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int3
     for (int j = 0; j < n; ++j) sum += counts[*first_row + j];
     return min((sum + n - 1) / n, kBins - 1);
   };
-  for (int i = threadIdx.x; i < kBins; i += blockDim.x) hist[i] = 0;
+  for (int i = threadIdx.x; i < kBins; i += blockDim.x) { hist[i] = 0; hist2[i] = 0; }
   __syncthreads();
   for (int blk = threadIdx.x; blk < n_blocks; blk += blockDim.x) {
     int first, rows;
     const int key = block_info(blk, &first, &rows);
     atomicAdd(&hist[key], rows);
+    atomicAdd(&hist2[key], (rows + 1) / 2);
   }
   __syncthreads();
   // exclusive prefix over descending bins: start[bin] = number of rows in blocks with a larger key
   if (threadIdx.x == 0) {
-    int run = 0;
-    for (int bin = kBins - 1; bin >= 0; --bin) { const int c = hist[bin]; hist[bin] = run; run += c; }
+    int run = 0, run2 = 0;
+    for (int bin = kBins - 1; bin >= 0; --bin) {
+      const int c = hist[bin]; hist[bin] = run; run += c;
+      const int c2 = hist2[bin]; hist2[bin] = run2; run2 += c2;
+    }
   }
   __syncthreads();
   for (int blk = threadIdx.x; blk < n_blocks; blk += blockDim.x) {
@@ -238,6 +244,9 @@ __global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int3
     const int key = block_info(blk, &first, &rows);
     const int pos = atomicAdd(&hist[key], rows);
     for (int j = 0; j < rows; ++j) order[pos + j] = first + j;
+    // a block starts at an even tile of its batch row (kRowChunk is even): its pairs are (first + 2j, first + 2j + 1)
+    const int pos2 = atomicAdd(&hist2[key], (rows + 1) / 2);
+    for (int j = 0; j < (rows + 1) / 2; ++j) pair_order[pos2 + j] = first + 2 * j;
   }
 }
 
@@ -253,7 +262,7 @@ void launch_schedule(bool kv_outer, const ScheduleArgs& a, int batch, cudaStream
   dim3 grid(a.n_outer_tiles, batch);
   if (kv_outer) schedule_kernel<true><<<grid, kTile, 0, s>>>(a);
   else schedule_kernel<false><<<grid, kTile, 0, s>>>(a);
-  order_kernel<<<1, 1024, 0, s>>>(a.counts, a.order, a.n_outer_tiles, batch);
+  order_kernel<<<1, 1024, 0, s>>>(a.counts, a.order, a.pair_order, a.n_outer_tiles, batch);
 }
 
 }  // namespace kvx

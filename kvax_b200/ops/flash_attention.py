@@ -29,6 +29,7 @@ counts allow it.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -54,6 +55,41 @@ def set_context_parallel_mode(mode: str) -> None:
 
 def get_context_parallel_mode() -> str:
     return _cp_mode
+
+
+# Optional phase timing of the context-parallel schedules: CUDA events around the exchange, mask and kernel
+# phases of a call, summed per name.  Off by default (no events are recorded).
+_phase_log: list | None = None
+
+
+def enable_phase_timing(on: bool = True) -> None:
+    """Starts (or stops and discards) the recording of per-phase CUDA events in the context-parallel paths."""
+    global _phase_log
+    _phase_log = [] if on else None
+
+
+def phase_times_ms() -> dict[str, float]:
+    """Milliseconds per phase name summed over everything recorded since `enable_phase_timing()`."""
+    out: dict[str, float] = {}
+    if _phase_log:
+        torch.cuda.synchronize()
+        for name, e0, e1 in _phase_log:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+    return out
+
+
+@contextlib.contextmanager
+def _phase(name: str):
+    if _phase_log is None:
+        yield
+        return
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    try:
+        yield
+    finally:
+        e1.record()
+        _phase_log.append((name, e0, e1))
 
 
 _BWD_MODES = ("fused", "two_kernel")
@@ -125,7 +161,8 @@ def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, sca
 
 
 def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: AttentionMask, fwd_blocks, scale,
-                      assume_sequential_positions=False, offsets=(0, 0), workspace=None, stages=0, out=None, lse=None):
+                      assume_sequential_positions=False, offsets=(0, 0), workspace=None, stages=0, out=None, lse=None,
+                      kernel=None):
     """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2, status) with lse2 (B, Hq, Sq)
     fp32, the base-2 log-sum-exp of the scaled scores, and the device's status word (a pinned
     host tensor; see `check_status`).  With `workspace` or `stages` the workspace is returned too."""
@@ -136,6 +173,7 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
     status, status_ptr = status_word(q.device)
     p = _lib.AttnFwdParams()
     p.stages = int(stages)
+    p.flags = {None: 0, "one_tile": _lib.FWD_ONE_TILE, "tile_pairs": _lib.FWD_TILE_PAIRS}[kernel]
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)
@@ -341,7 +379,8 @@ def _exchange_seq_to_heads(tensors, cp: int, rank: int, group, permuted: bool):
         B, Sl, H, D = x.shape
         assert B == 1 and Sl % 2 == 0
         hl, half = H // cp, Sl // 2
-        send = _regroup_heads(x, cp, True)                       # (cp, 1, Sl, hl, D)
+        with _phase("regroup"):
+            send = _regroup_heads(x, cp, True)                   # (cp, 1, Sl, hl, D)
         nat = torch.empty((1, cp * Sl, hl, D), dtype=x.dtype, device=x.device)
         outs.append(nat)
         for r in range(cp):
@@ -354,11 +393,13 @@ def _exchange_seq_to_heads(tensors, cp: int, rank: int, group, permuted: bool):
                 else:
                     ops.append(dist.P2POp(dist.isend, src, ranks[r], group))
                     ops.append(dist.P2POp(dist.irecv, dst, ranks[r], group))
-    for dst, src in local_copies:
-        dst.copy_(src)
-    if ops:
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
+    with _phase("local_copy"):
+        for dst, src in local_copies:
+            dst.copy_(src)
+    with _phase("p2p"):
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
     return outs
 
 
@@ -387,12 +428,15 @@ def _exchange_heads_to_seq(tensors, cp: int, rank: int, group, permuted: bool):
                 else:
                     ops.append(dist.P2POp(dist.isend, src, ranks[r], group))
                     ops.append(dist.P2POp(dist.irecv, dst, ranks[r], group))
-    for dst, src in local_copies:
-        dst.copy_(src)
-    if ops:
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
-    return [_regroup_heads(r_, cp, False) for r_ in recvs]
+    with _phase("local_copy"):
+        for dst, src in local_copies:
+            dst.copy_(src)
+    with _phase("p2p"):
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+    with _phase("regroup"):
+        return [_regroup_heads(r_, cp, False) for r_ in recvs]
 
 
 def _fast_exchange_ok(x: torch.Tensor) -> bool:
@@ -406,14 +450,16 @@ class _FlashAttention(torch.autograd.Function):
     def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, masks, scale, fwd_params, bwd_params,
                 sequential, permuted, cp, rank, group):
         if cp > 1:
-            k_full = _gather_kv(key, cp, group, permuted)
-            v_full = _gather_kv(value, cp, group, permuted)
+            with _phase("gather_kv"):
+                k_full = _gather_kv(key, cp, group, permuted)
+                v_full = _gather_kv(value, cp, group, permuted)
         else:
             k_full, v_full = key, value
         offsets = context_offsets(rank, cp, query.shape[1], permuted)
-        out, lse, status = attention_forward(
-            query, k_full, v_full, q_pos, q_seg, kv_pos, kv_seg, masks[0],
-            (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, offsets)
+        with _phase("attention_forward"):
+            out, lse, status = attention_forward(
+                query, k_full, v_full, q_pos, q_seg, kv_pos, kv_seg, masks[0],
+                (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, offsets)
         ctx.save_for_backward(query, k_full, v_full, out, lse, q_pos, q_seg, kv_pos, kv_seg,
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = len(masks)
@@ -433,11 +479,13 @@ class _FlashAttention(torch.autograd.Function):
         bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
         if query.shape[1] % bq or k_full.shape[1] % bk:
             raise AssertionError("sequence lengths must be divisible by the backward block sizes")
-        dq, dk, dv, _ = attention_backward(query, k_full, v_full, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg,
-                                           masks[1], masks[2], (bq, bk), scale, sequential, offsets)
+        with _phase("attention_backward"):
+            dq, dk, dv, _ = attention_backward(query, k_full, v_full, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg,
+                                               masks[1], masks[2], (bq, bk), scale, sequential, offsets)
         if cp > 1:
-            dk = _scatter_dkv(dk, cp, group, permuted, kv_dtype)
-            dv = _scatter_dkv(dv, cp, group, permuted, kv_dtype)
+            with _phase("scatter_dkv"):
+                dk = _scatter_dkv(dk, cp, group, permuted, kv_dtype)
+                dv = _scatter_dkv(dv, cp, group, permuted, kv_dtype)
         else:
             dk, dv = dk.to(kv_dtype), dv.to(kv_dtype)
         return (dq, dk, dv) + (None,) * 13
@@ -461,16 +509,19 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
             q_h = _seq_to_heads(query, cp, group, permuted)
             k_h = _seq_to_heads(key, cp, group, permuted)
             v_h = _seq_to_heads(value, cp, group, permuted)
-        q_pos_f = _gather_tokens(q_pos, cp, group, permuted)
-        q_seg_f = _gather_tokens(q_seg, cp, group, permuted)
+        with _phase("gather_tokens"):
+            q_pos_f = _gather_tokens(q_pos, cp, group, permuted)
+            q_seg_f = _gather_tokens(q_seg, cp, group, permuted)
         specs = [(fwd_params.query_block_size, fwd_params.kv_block_size, False)]
         if n_masks == 3:
             specs.append((bwd_params.kv_block_size, bwd_params.query_block_size, False))
             specs.append((bwd_params.query_block_size, bwd_params.kv_block_size, True))
-        masks = build_masks(q_pos_f, q_seg_f, kv_pos, kv_seg, specs, True)
-        out_h, lse_h, status = attention_forward(
-            q_h, k_h, v_h, q_pos_f, q_seg_f, kv_pos, kv_seg, masks[0],
-            (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, (0, 0))
+        with _phase("build_masks"):
+            masks = build_masks(q_pos_f, q_seg_f, kv_pos, kv_seg, specs, True)
+        with _phase("attention_forward"):
+            out_h, lse_h, status = attention_forward(
+                q_h, k_h, v_h, q_pos_f, q_seg_f, kv_pos, kv_seg, masks[0],
+                (fwd_params.query_block_size, fwd_params.kv_block_size), scale, sequential, (0, 0))
         ctx.save_for_backward(q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = n_masks
@@ -496,8 +547,9 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
             dout_h = _exchange_seq_to_heads((dout,), cp, rank, group, permuted)[0]
         else:
             dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
-        dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
-                                                 masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
+        with _phase("attention_backward"):
+            dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
+                                                     masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
         # every dK / dV element is complete on this rank: cast first, then exchange
         if fast:
             dq, dk, dv = _exchange_heads_to_seq((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), cp, rank, group, permuted)

@@ -10,6 +10,17 @@ from oracle import generators as gen
 
 pytestmark = pytest.mark.gpu
 
+_KERNEL = None
+
+
+@pytest.fixture(autouse=True, params=["one_tile", "tile_pairs"])
+def fwd_kernel(request):
+    """Every test of this file runs on both forward kernels (a CTA per query tile / per pair of query tiles)."""
+    global _KERNEL
+    _KERNEL = request.param
+    yield request.param
+    _KERNEL = None
+
 
 def _run_fwd(inp, fwd_blocks=(128, 128), sequential=False, q_slice=None, kv_slice=None):
     import kvax_b200 as kv
@@ -22,7 +33,8 @@ def _run_fwd(inp, fwd_blocks=(128, 128), sequential=False, q_slice=None, kv_slic
     qp, qsg = i32_cuda(inp["positions"][:, qs]), i32_cuda(inp["segment_ids"][:, qs])
     kp, ksg = i32_cuda(inp["positions"][:, ks]), i32_cuda(inp["segment_ids"][:, ks])
     (mask,) = build_masks(qp, qsg, kp, ksg, [(fwd_blocks[0], fwd_blocks[1], False)], True)
-    out, lse, status = attention_forward(q, k, v, qp, qsg, kp, ksg, mask, fwd_blocks, inp["scale"], sequential)
+    out, lse, status = attention_forward(q, k, v, qp, qsg, kp, ksg, mask, fwd_blocks, inp["scale"], sequential,
+                                         kernel=_KERNEL)
     torch.cuda.synchronize()
     check_status(status, "attn_fwd")
     return out.float().cpu().numpy(), lse.cpu().numpy()

@@ -15,8 +15,9 @@ pytestmark = pytest.mark.gpu
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attn_*.npz")))
 
 
+@pytest.mark.parametrize("fwd_kernel", ["one_tile", "tile_pairs"])
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[5:-4] for p in GOLDEN])
-def test_kernels_match_reference_outputs(path):
+def test_kernels_match_reference_outputs(path, fwd_kernel):
     from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status, context_offsets
     from kvax_b200.ops.mask_creator import build_masks
 
@@ -36,7 +37,7 @@ def test_kernels_match_reference_outputs(path):
         bq, bk = (int(x) for x in z["bwd"])
         specs += [(bk, bq, False), (bq, bk, True)]
     masks = build_masks(qp, qs, kp, ks, specs, True)
-    out, lse, st = attention_forward(q, k, v, qp, qs, kp, ks, masks[0], fwd, scale, seq, offsets)
+    out, lse, st = attention_forward(q, k, v, qp, qs, kp, ks, masks[0], fwd, scale, seq, offsets, kernel=fwd_kernel)
     torch.cuda.synchronize()
     check_status(st, "attn_fwd")
     rows = (z["q_seg"] != -1) & np.isfinite(z["lse2"]).all(axis=1)
