@@ -135,6 +135,40 @@ int kvax_b200_permute_tokens(const void* src, void* dst, int64_t batch, int64_t 
 int kvax_b200_regroup_heads(const void* src, void* dst, int64_t tokens, int32_t cp, int32_t heads_per_group,
                             int64_t head_bytes, int32_t to_groups, kvax_b200_stream_t stream);
 
+/* Head exchange over peer memory (no counterpart in the reference; it moves the data the
+ * reference's all-gather of K / V moves, flash_attention_triton.py:2064-2115, for the
+ * head-exchange schedule): one kernel reads a tensor of this GPU and stores every token's heads
+ * straight into the landing buffers of the ranks that own them, over NVLink, already in the layout
+ * the attention kernels read.
+ *
+ * Landing buffers are allocated by `peer_buffer_alloc` (cudaMalloc), made known to the other
+ * processes of the node with `peer_buffer_export` (a CUDA IPC handle of
+ * KVAX_B200_PEER_HANDLE_BYTES bytes, carried by the caller, e.g. through torch.distributed) and
+ * `peer_buffer_open`.  `peer_buffers[r]` is rank r's buffer as this process addresses it
+ * (`peer_buffers[rank]` the own one), `dst_offset_bytes` the place of this tensor inside every
+ * buffer.  The batch is 1 and `local_tokens` even (two half-sequences per rank).
+ *   to_heads = 1: src (local_tokens, cp * heads_per_rank, D) -> rank r gets heads
+ *                 [r * heads_per_rank, ...) of these tokens at their natural token position
+ *                 in its (cp * local_tokens, heads_per_rank, D) buffer;
+ *   to_heads = 0: src (cp * local_tokens, heads_per_rank, D) in natural token order -> rank r
+ *                 gets its tokens into heads [rank * heads_per_rank, ...) of its
+ *                 (local_tokens, cp * heads_per_rank, D) buffer.
+ * `permuted`: the local tokens of rank r are chunks r and 2 cp - 1 - r of the natural order
+ * (kvax/utils/permutation.py:9-42), else chunks 2r and 2r + 1.
+ * The kernel waits for nobody.  The caller orders it on the stream against the peers: nobody
+ * may still read the destination region when it starts, and a rank may read its own buffer once
+ * all ranks' kernels have completed (a collective on the same stream on both sides). */
+#define KVAX_B200_MAX_PEERS 16
+#define KVAX_B200_PEER_HANDLE_BYTES 64
+int kvax_b200_peer_buffer_alloc(size_t bytes, void** ptr);
+int kvax_b200_peer_buffer_free(void* ptr);
+int kvax_b200_peer_buffer_export(void* ptr, unsigned char handle[KVAX_B200_PEER_HANDLE_BYTES]);
+int kvax_b200_peer_buffer_open(const unsigned char handle[KVAX_B200_PEER_HANDLE_BYTES], void** peer_ptr);
+int kvax_b200_peer_buffer_close(void* peer_ptr);
+int kvax_b200_head_exchange(const void* src, void* const* peer_buffers, int64_t dst_offset_bytes, int64_t local_tokens,
+                            int32_t cp, int32_t rank, int32_t heads_per_rank, int64_t head_bytes, int32_t permuted,
+                            int32_t to_heads, kvax_b200_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Flash attention, forward and backward.
  * ---------------------------------------------------------------------------------- */

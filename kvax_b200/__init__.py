@@ -13,10 +13,12 @@ from kvax_b200.ops import (
     flash_attention,
     get_backward_mode,
     get_context_parallel_mode,
+    get_head_exchange_transport,
     last_status,
     print_mask,
     set_backward_mode,
     set_context_parallel_mode,
+    set_head_exchange_transport,
 )
 from kvax_b200.utils import (
     PADDING_SEGMENT_ID,

@@ -18,6 +18,12 @@ EXPORTS = (
     "kvax_b200_mask_build_static",
     "kvax_b200_permute_tokens",
     "kvax_b200_regroup_heads",
+    "kvax_b200_peer_buffer_alloc",
+    "kvax_b200_peer_buffer_free",
+    "kvax_b200_peer_buffer_export",
+    "kvax_b200_peer_buffer_open",
+    "kvax_b200_peer_buffer_close",
+    "kvax_b200_head_exchange",
     "kvax_b200_attn_fwd_workspace_bytes",
     "kvax_b200_attn_fwd",
     "kvax_b200_attn_bwd_workspace_bytes",
@@ -27,7 +33,8 @@ EXPORTS = (
 )
 
 BWD_TWO_KERNEL = 1
-FWD_ONE_TILE, FWD_TILE_PAIRS = 1, 2          # kvax_b200_attn_bwd_params.flags
+FWD_ONE_TILE, FWD_TILE_PAIRS = 1, 2          # kvax_b200_attn_fwd_params.flags
+MAX_PEERS, PEER_HANDLE_BYTES = 16, 64
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -98,6 +105,18 @@ def load() -> C.CDLL:
     lib.kvax_b200_permute_tokens.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp]
     lib.kvax_b200_regroup_heads.restype = C.c_int
     lib.kvax_b200_regroup_heads.argtypes = [vp, vp, i64, i32, i32, i64, i32, vp]
+    lib.kvax_b200_peer_buffer_alloc.restype = C.c_int
+    lib.kvax_b200_peer_buffer_alloc.argtypes = [C.c_size_t, C.POINTER(vp)]
+    lib.kvax_b200_peer_buffer_free.restype = C.c_int
+    lib.kvax_b200_peer_buffer_free.argtypes = [vp]
+    lib.kvax_b200_peer_buffer_export.restype = C.c_int
+    lib.kvax_b200_peer_buffer_export.argtypes = [vp, C.c_char_p]
+    lib.kvax_b200_peer_buffer_open.restype = C.c_int
+    lib.kvax_b200_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    lib.kvax_b200_peer_buffer_close.restype = C.c_int
+    lib.kvax_b200_peer_buffer_close.argtypes = [vp]
+    lib.kvax_b200_head_exchange.restype = C.c_int
+    lib.kvax_b200_head_exchange.argtypes = [vp, C.POINTER(vp), i64, i64, i32, i32, i32, i64, i32, i32, vp]
     lib.kvax_b200_attn_fwd_workspace_bytes.restype = C.c_size_t
     lib.kvax_b200_attn_fwd_workspace_bytes.argtypes = [C.POINTER(AttnFwdParams)]
     lib.kvax_b200_attn_fwd.restype = C.c_int

@@ -57,6 +57,37 @@ def get_context_parallel_mode() -> str:
     return _cp_mode
 
 
+_HX_TRANSPORTS = ("auto", "peer", "nccl")
+_hx_transport = "auto"
+
+
+def set_head_exchange_transport(mode: str) -> None:
+    """How the head exchange moves data between the GPUs of a node.  "peer": one kernel per tensor that stores
+    straight into landing buffers in the peers' memory (CUDA IPC, NVLink); "nccl": grouped NCCL sends and
+    receives; "auto" (default): peer memory when the buffers can be shared, else NCCL."""
+    global _hx_transport
+    if mode not in _HX_TRANSPORTS:
+        raise ValueError(f"unknown head-exchange transport {mode!r}; expected one of {_HX_TRANSPORTS}")
+    _hx_transport = mode
+
+
+def get_head_exchange_transport() -> str:
+    return _hx_transport
+
+
+def _exchange(tensors, to_heads: bool, cp: int, rank: int, group, permuted: bool):
+    """Zero-copy head exchange of batch-1 tensors by the chosen transport."""
+    if _hx_transport != "nccl":
+        from kvax_b200.ops import _peer
+        outs = _peer.exchange(tensors, to_heads, cp, rank, group, permuted, _phase)
+        if outs is not None:
+            return outs
+        if _hx_transport == "peer":
+            raise RuntimeError("head-exchange transport \"peer\": the landing buffers cannot be shared between the ranks")
+    fn = _exchange_seq_to_heads if to_heads else _exchange_heads_to_seq
+    return fn(tensors, cp, rank, group, permuted)
+
+
 # Optional phase timing of the context-parallel schedules: CUDA events around the exchange, mask and kernel
 # phases of a call, summed per name.  Off by default (no events are recorded).
 _phase_log: list | None = None
@@ -504,7 +535,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         rank = torch.distributed.get_rank(group)
         fast = _fast_exchange_ok(query) and _fast_exchange_ok(key) and _fast_exchange_ok(value)
         if fast:
-            q_h, k_h, v_h = _exchange_seq_to_heads((query, key, value), cp, rank, group, permuted)
+            q_h, k_h, v_h = _exchange((query, key, value), True, cp, rank, group, permuted)
         else:
             q_h = _seq_to_heads(query, cp, group, permuted)
             k_h = _seq_to_heads(key, cp, group, permuted)
@@ -527,7 +558,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         ctx.n_masks = n_masks
         ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype, rank, fast)
         if fast:
-            return _exchange_heads_to_seq((out_h,), cp, rank, group, permuted)[0]
+            return _exchange((out_h,), False, cp, rank, group, permuted)[0]
         return _heads_to_seq(out_h, cp, group, permuted)
 
     @staticmethod
@@ -544,7 +575,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         if q_h.shape[1] % bq or k_h.shape[1] % bk:
             raise AssertionError("sequence lengths must be divisible by the backward block sizes")
         if fast:
-            dout_h = _exchange_seq_to_heads((dout,), cp, rank, group, permuted)[0]
+            dout_h = _exchange((dout,), True, cp, rank, group, permuted)[0]
         else:
             dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
         with _phase("attention_backward"):
@@ -552,7 +583,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
                                                      masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
         # every dK / dV element is complete on this rank: cast first, then exchange
         if fast:
-            dq, dk, dv = _exchange_heads_to_seq((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), cp, rank, group, permuted)
+            dq, dk, dv = _exchange((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), False, cp, rank, group, permuted)
             return (dq, dk, dv) + (None,) * 12
         dq = _heads_to_seq(dq_h, cp, group, permuted)
         dk = _heads_to_seq(dk_h.to(kv_dtype), cp, group, permuted)

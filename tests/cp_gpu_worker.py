@@ -151,6 +151,13 @@ def main():
     res["fused_docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=4, hkv=2, pad=0.05, sequential=False)
     res["fused_hx_docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=world, pad=0.05,
                                        sequential=False, mode="head_exchange")
+    # the same exchange through grouped NCCL sends / receives instead of peer-memory stores
+    kv.set_head_exchange_transport("nccl")
+    res["fused_hx_docmask_nccl"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=world, pad=0.05,
+                                            sequential=False, mode="head_exchange")
+    kv.set_head_exchange_transport("auto")
+    from kvax_b200.ops import _peer
+    res["peer_memory_transport"] = "used" if any(a for a in _peer._arenas.values()) else "not available: NCCL transport used"
     kv.set_backward_mode("two_kernel")
     res["docmask"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=4, hkv=2, pad=0.05, sequential=False)
     res["batch2_seqpos"] = run_case(rank, world, dev, seq=512 * world, batch=2, hq=2, hkv=2, pad=0.0, sequential=True)

@@ -25,3 +25,4 @@ def test_context_parallel_matches_single_gpu():
     res = _launch(world)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "cp gpu worker ok" in res.stdout
+    print(res.stdout[-1500:])
