@@ -37,7 +37,7 @@ enum {
   KVAX_B200_ESCRATCH = -6     /* problem needs more than the library's built-in scratch area */
 };
 
-enum { KVAX_B200_BF16 = 0 };
+enum { KVAX_B200_BF16 = 0, KVAX_B200_F16 = 1 };   /* operand (and output) type of the attention kernels */
 
 #define KVAX_B200_PADDING_SEGMENT_ID (-1) /* kvax/utils/common.py:9 */
 
@@ -185,7 +185,7 @@ typedef struct kvax_b200_attn_shape {
   int32_t batch, q_len, kv_len;
   int32_t q_heads, kv_heads;
   int32_t head_dim;        /* Dqk == Dv; 64 or 128                                       */
-  int32_t dtype;           /* KVAX_B200_BF16                                             */
+  int32_t dtype;           /* KVAX_B200_BF16 or KVAX_B200_F16: q, k, v, out, dout, dq            */
   int32_t assume_sequential_positions; /* causal test on indices + query_global_offset   */
   float scale;
   int32_t reserved;

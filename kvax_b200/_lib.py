@@ -35,6 +35,7 @@ EXPORTS = (
 BWD_TWO_KERNEL = 1
 FWD_ONE_TILE, FWD_TILE_PAIRS = 1, 2          # kvax_b200_attn_fwd_params.flags
 MAX_PEERS, PEER_HANDLE_BYTES = 16, 64
+DTYPE_BF16, DTYPE_F16 = 0, 1               # kvax_b200_attn_shape.dtype
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 

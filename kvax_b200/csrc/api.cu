@@ -34,7 +34,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 // bf16 tensor (batch, seq, heads, D) with element strides {batch, seq, head}; boxes of
 // 128 rows x 64 columns of one head, 128-byte swizzle, out-of-range rows read as zero.
-int make_tmap(CUtensorMap* map, const void* base, int batch, int seq, int heads, int d, const int64_t* strides) {
+int make_tmap(CUtensorMap* map, const void* base, int batch, int seq, int heads, int d, const int64_t* strides, int dtype) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return KVAX_B200_ENODEVICE;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((strides[0] | strides[1] | strides[2]) & 7)) return KVAX_B200_EUNSUPPORTED;
@@ -42,7 +42,8 @@ int make_tmap(CUtensorMap* map, const void* base, int batch, int seq, int heads,
   cuuint64_t gstr[3] = {cuuint64_t(strides[2]) * 2, cuuint64_t(strides[1]) * 2, cuuint64_t(strides[0]) * 2};
   cuuint32_t box[4] = {64, 1, cuuint32_t(kTile), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, gstr, box, estr,
+  const CUtensorMapDataType elem = dtype == KVAX_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, elem, 4, const_cast<void*>(base), dims, gstr, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
@@ -65,7 +66,7 @@ int make_tmap_acc(CUtensorMap* map, float* base, int batch, int seq, int heads, 
 int check_shape(const kvax_b200_attn_shape& s) {
   if (s.batch <= 0 || s.q_len <= 0 || s.kv_len <= 0 || s.q_heads <= 0 || s.kv_heads <= 0) return KVAX_B200_EINVAL;
   if (s.q_heads % s.kv_heads) return KVAX_B200_EINVAL;
-  if (s.dtype != KVAX_B200_BF16) return KVAX_B200_EUNSUPPORTED;
+  if (s.dtype != KVAX_B200_BF16 && s.dtype != KVAX_B200_F16) return KVAX_B200_EUNSUPPORTED;
   if (s.head_dim != 64 && s.head_dim != 128) return KVAX_B200_EUNSUPPORTED;
   if (!s.q_segment_ids || !s.kv_segment_ids) return KVAX_B200_EINVAL;
   if (!s.assume_sequential_positions && (!s.q_positions || !s.kv_positions)) return KVAX_B200_EINVAL;
@@ -190,9 +191,9 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   if (!(stages & 2)) return KVAX_B200_OK;
 
   FwdLaunch L;
-  rc = make_tmap(&L.tmap_q, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);  if (rc) return rc;
-  rc = make_tmap(&L.tmap_k, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides); if (rc) return rc;
-  rc = make_tmap(&L.tmap_v, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides); if (rc) return rc;
+  rc = make_tmap(&L.tmap_q, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides, s.dtype);  if (rc) return rc;
+  rc = make_tmap(&L.tmap_k, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides, s.dtype); if (rc) return rc;
+  rc = make_tmap(&L.tmap_v, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides, s.dtype); if (rc) return rc;
   FwdArgs& a = L.args;
   fill_list(&a.list, sa);
   a.mask = mv; a.tok = sa.tok;
@@ -200,7 +201,7 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   for (int i = 0; i < 3; ++i) a.o_strides[i] = s.o_strides[i];
   a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
-  L.batch = s.batch; L.head_dim = s.head_dim;
+  L.batch = s.batch; L.head_dim = s.head_dim; L.dtype = s.dtype;
   // Two query tiles per CTA halve the K / V traffic and pay on long sequences; short ones have too few and too uneven
   // CTAs that way (measured: 8k tokens 20 % slower, 16k dense 7 % faster, 32k document masks the same).
   bool pairs = s.kv_len >= 16384;
@@ -278,16 +279,16 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   long long ostr[3] = {s.o_strides[0], s.o_strides[1], s.o_strides[2]};
   if (stages & 2) {
     rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
-                               dq_acc, ostr, s.batch, s.q_len, s.q_heads, s.head_dim, st);
+                               dq_acc, ostr, s.batch, s.q_len, s.q_heads, s.head_dim, s.dtype, st);
     if (rc) return rc;
   }
   if (!(stages & (4 | 8 | 16 | 32))) return KVAX_B200_OK;
 
   CUtensorMap tq, tk, tv, tdo;
-  rc = make_tmap(&tq, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides);     if (rc) return rc;
-  rc = make_tmap(&tk, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides);   if (rc) return rc;
-  rc = make_tmap(&tv, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides);   if (rc) return rc;
-  rc = make_tmap(&tdo, p->dout, s.batch, s.q_len, s.q_heads, s.head_dim, s.o_strides); if (rc) return rc;
+  rc = make_tmap(&tq, p->q, s.batch, s.q_len, s.q_heads, s.head_dim, s.q_strides, s.dtype);     if (rc) return rc;
+  rc = make_tmap(&tk, p->k, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.k_strides, s.dtype);   if (rc) return rc;
+  rc = make_tmap(&tv, p->v, s.batch, s.kv_len, s.kv_heads, s.head_dim, s.v_strides, s.dtype);   if (rc) return rc;
+  rc = make_tmap(&tdo, p->dout, s.batch, s.q_len, s.q_heads, s.head_dim, s.o_strides, s.dtype); if (rc) return rc;
 
   BwdArgs a;
   a.tok = tok; a.lse = p->lse; a.delta = delta;
@@ -306,18 +307,18 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
       F.tmap_k = tk; F.tmap_v = tv; F.tmap_q = tq; F.tmap_do = tdo;
       rc = make_tmap_acc(&F.tmap_dq, dq_acc, s.batch, s.q_len, s.q_heads, s.head_dim);
       if (rc) return rc;
-      F.batch = s.batch; F.head_dim = s.head_dim;
+      F.batch = s.batch; F.head_dim = s.head_dim; F.dtype = s.dtype;
       rc = launch_attn_bwd_fused(F, st);
       if (rc) return rc;
     }
     if (stages & 32)
-      return launch_attn_bwd_dq_cast(dq_acc, a.dq, dq_strides, s.batch, s.q_len, s.q_heads, s.head_dim, s.scale, st);
+      return launch_attn_bwd_dq_cast(dq_acc, a.dq, dq_strides, s.batch, s.q_len, s.q_heads, s.head_dim, s.scale, s.dtype, st);
     return KVAX_B200_OK;
   }
 
   BwdLaunch L;
   L.args = a;
-  L.batch = s.batch; L.head_dim = s.head_dim;
+  L.batch = s.batch; L.head_dim = s.head_dim; L.dtype = s.dtype;
   // dQ: resident Q, dO of one query tile; streams K, V
   fill_list(&L.args.list, sq);
   L.args.mask = mv_dq;

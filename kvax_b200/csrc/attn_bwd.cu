@@ -23,6 +23,8 @@
 //
 // Semantics follow flash_attention_backward_kernel_dquery (:620-871),
 // flash_attention_backward_kernel_dkdv (:874-1191) and attn_bwd_preprocess (:373-410).
+#include <cuda_fp16.h>
+
 #include "attn_common.cuh"
 #include "internal.h"
 #include "ptx.cuh"
@@ -75,7 +77,7 @@ struct KvSmem {
   static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
-template <int D>
+template <int D, bool kF16>
 __global__ void __launch_bounds__(kKvThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
@@ -219,8 +221,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     }
   } else if (warp == kKvMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
-    constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
+    constexpr uint32_t idesc_t = make_idesc_16(kTile, kTile, 0, 0, kF16);
+    constexpr uint32_t idesc_acc = make_idesc_16(kTile, D, 0, 1, kF16);
     const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
     const uint32_t ybase = smem_u32(smem + L::kY);
     const int n = __shfl_sync(0xffffffffu, n_items, 0);
@@ -345,7 +347,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       {
         uint32_t pk[16];
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1]));
+        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack16<kF16>(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1]));
         tmem_st16(my_t1, pk);
       }
       tmem_st_wait();
@@ -368,8 +370,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
           const float d1 = __uint_as_float(v[jj + 1]) * (__uint_as_float(dp[jj + 1]) - dl.y);
           const float d2 = __uint_as_float(v[jj + 2]) * (__uint_as_float(dp[jj + 2]) - dl.z);
           const float d3 = __uint_as_float(v[jj + 3]) * (__uint_as_float(dp[jj + 3]) - dl.w);
-          ds[jj >> 1] = pack_bf16(d0, d1);
-          ds[(jj >> 1) + 1] = pack_bf16(d2, d3);
+          ds[jj >> 1] = pack16<kF16>(d0, d1);
+          ds[(jj >> 1) + 1] = pack16<kF16>(d2, d3);
         }
         tmem_st16(my_t2, ds);      // over the first 16 of this thread's 32 dP columns, all of which are in registers
       }
@@ -447,7 +449,7 @@ struct DqSmem {
   static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
-template <int D>
+template <int D, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -529,8 +531,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);
-    constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, D, 0, 1);
+    constexpr uint32_t idesc_t = make_idesc_16(kTile, kTile, 0, 0, kF16);
+    constexpr uint32_t idesc_acc = make_idesc_16(kTile, D, 0, 1, kF16);
     const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
     const uint32_t kbase = smem_u32(smem + L::kK), vbase = smem_u32(smem + L::kV);
     const int n = __shfl_sync(0xffffffffu, n_items, 0);
@@ -664,7 +666,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int jj = 0; jj < 32; jj += 2) {
           const float d0 = __uint_as_float(v[ch][jj]) * (__uint_as_float(dp[ch][jj]) - delta);
           const float d1 = __uint_as_float(v[ch][jj + 1]) * (__uint_as_float(dp[ch][jj + 1]) - delta);
-          ds[jj >> 1] = pack_bf16(d0, d1);
+          ds[jj >> 1] = pack16<kF16>(d0, d1);
         }
         tmem_st16(my_t1 + ch * 16, ds);
       }
@@ -685,10 +687,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
           for (int jj = 0; jj < 32; jj += 8) {
             uint4 w;
-            w.x = pack_bf16(__uint_as_float(v[jj + 0]) * a.scale, __uint_as_float(v[jj + 1]) * a.scale);
-            w.y = pack_bf16(__uint_as_float(v[jj + 2]) * a.scale, __uint_as_float(v[jj + 3]) * a.scale);
-            w.z = pack_bf16(__uint_as_float(v[jj + 4]) * a.scale, __uint_as_float(v[jj + 5]) * a.scale);
-            w.w = pack_bf16(__uint_as_float(v[jj + 6]) * a.scale, __uint_as_float(v[jj + 7]) * a.scale);
+            w.x = pack16<kF16>(__uint_as_float(v[jj + 0]) * a.scale, __uint_as_float(v[jj + 1]) * a.scale);
+            w.y = pack16<kF16>(__uint_as_float(v[jj + 2]) * a.scale, __uint_as_float(v[jj + 3]) * a.scale);
+            w.z = pack16<kF16>(__uint_as_float(v[jj + 4]) * a.scale, __uint_as_float(v[jj + 5]) * a.scale);
+            w.w = pack16<kF16>(__uint_as_float(v[jj + 6]) * a.scale, __uint_as_float(v[jj + 7]) * a.scale);
             reinterpret_cast<uint4*>(dq_row)[(ch * 32 + jj) >> 3] = w;
           }
         }
@@ -715,7 +717,7 @@ template <int D>
 __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                                             const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                                                             float* __restrict__ dq_acc, long long sb, long long ss,
-                                                            long long sh, int batch, int seq, int heads) {
+                                                            long long sh, int batch, int seq, int heads, int f16) {
   constexpr int kLanes = D / 8, kRowsPerWarp = 32 / kLanes;
   const int lane = threadIdx.x & 31;
   const int sub = lane / kLanes, li = lane % kLanes;
@@ -735,11 +737,17 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
         z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
         z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
-      const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        const float2 xf = __bfloat1622float2(xp[t]), yf = __bfloat1622float2(yp[t]);
+        float2 xf, yf;
+        if (f16) {
+          xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[t]));
+          yf = __half22float2(*reinterpret_cast<const __half2*>(&yw[t]));
+        } else {
+          xf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[t]));
+          yf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yw[t]));
+        }
         acc = fmaf(xf.x, yf.x, acc);
         acc = fmaf(xf.y, yf.y, acc);
       }
@@ -750,20 +758,20 @@ __global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16
   }
 }
 
-template <int D>
+template <int D, bool kF16>
 int launch_dkdv(const BwdLaunch& L, cudaStream_t stream) {
   constexpr int smem = KvSmem<D>::kTotal;
-  auto kern = attn_bwd_dkdv_kernel<D>;
+  auto kern = attn_bwd_dkdv_kernel<D, kF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
   dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
   kern<<<grid, kKvThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // K, V, Q, dO
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
 
-template <int D>
+template <int D, bool kF16>
 int launch_dq(const BwdLaunch& L, cudaStream_t stream) {
   constexpr int smem = DqSmem<D>::kTotal;
-  auto kern = attn_bwd_dq_kernel<D>;
+  auto kern = attn_bwd_dq_kernel<D, kF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
   dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.q_heads, 1, 1);
   kern<<<grid, kThreads, smem, stream>>>(L.tmap_x1, L.tmap_x2, L.tmap_y1, L.tmap_y2, L.args);   // Q, dO, K, V
@@ -773,21 +781,28 @@ int launch_dq(const BwdLaunch& L, cudaStream_t stream) {
 }  // namespace
 
 int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream) {
-  if (L.head_dim == 128) return kv_outer ? launch_dkdv<128>(L, stream) : launch_dq<128>(L, stream);
-  if (L.head_dim == 64) return kv_outer ? launch_dkdv<64>(L, stream) : launch_dq<64>(L, stream);
+  if (L.dtype == KVAX_B200_F16) {
+    if (L.head_dim == 128) return kv_outer ? launch_dkdv<128, true>(L, stream) : launch_dq<128, true>(L, stream);
+    if (L.head_dim == 64) return kv_outer ? launch_dkdv<64, true>(L, stream) : launch_dq<64, true>(L, stream);
+    return KVAX_B200_EUNSUPPORTED;
+  }
+  if (L.head_dim == 128) return kv_outer ? launch_dkdv<128, false>(L, stream) : launch_dq<128, false>(L, stream);
+  if (L.head_dim == 64) return kv_outer ? launch_dkdv<64, false>(L, stream) : launch_dq<64, false>(L, stream);
   return KVAX_B200_EUNSUPPORTED;
 }
 
 int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, float* dq_acc,
-                          const long long* strides, int batch, int seq, int heads, int head_dim, cudaStream_t stream) {
+                          const long long* strides, int batch, int seq, int heads, int head_dim, int dtype,
+                          cudaStream_t stream) {
+  const int f16 = dtype == KVAX_B200_F16;
   const long long rows = (long long)batch * seq * heads;
   const int rows_per_warp = 32 / (head_dim / 8);
   long long blocks = (rows / rows_per_warp + 7) / 8 + 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (head_dim == 128)
-    attn_bwd_delta_kernel<128><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads);
+    attn_bwd_delta_kernel<128><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads, f16);
   else if (head_dim == 64)
-    attn_bwd_delta_kernel<64><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads);
+    attn_bwd_delta_kernel<64><<<int(blocks), 256, 0, stream>>>(o, d_o, delta, dq_acc, strides[0], strides[1], strides[2], batch, seq, heads, f16);
   else
     return KVAX_B200_EUNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;

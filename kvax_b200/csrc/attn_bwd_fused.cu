@@ -98,7 +98,7 @@ struct FusedSmem {
   static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
-template <int D>
+template <int D, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                       const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
@@ -238,10 +238,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     PH_END(3, n)
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    constexpr uint32_t idesc_t = make_idesc_bf16(kTile, kTile, 0, 0);    // X (K-major) x Y (K-major)
-    constexpr uint32_t idesc_dv = make_idesc_bf16(kTile, D, 0, 1);       // P^T (TMEM) x dO (N-major)
-    constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, D, 1, 1);       // dS^T tile (MN-major A) x K tile (MN-major B)
-    constexpr uint32_t idesc_dk = make_idesc_bf16(kTile, D, 0, 1);       // dS^T tile (K-major A) x Q (N-major B)
+    constexpr uint32_t idesc_t = make_idesc_16(kTile, kTile, 0, 0, kF16);    // X (K-major) x Y (K-major)
+    constexpr uint32_t idesc_dv = make_idesc_16(kTile, D, 0, 1, kF16);       // P^T (TMEM) x dO (N-major)
+    constexpr uint32_t idesc_dq = make_idesc_16(kTile, D, 1, 1, kF16);       // dS^T tile (MN-major A) x K tile (MN-major B)
+    constexpr uint32_t idesc_dk = make_idesc_16(kTile, D, 0, 1, kF16);       // dS^T tile (K-major A) x Q (N-major B)
     const uint32_t x1_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), 16), x2_lo = sdesc_lo_sw128(smem_u32(smem + L::kX2), 16);
     const uint32_t kmn_lo = sdesc_lo_sw128(smem_u32(smem + L::kX1), L::kBoxBytes);   // K tile with kv as the contraction index
     const uint32_t qbase = smem_u32(smem + L::kQ);
@@ -435,7 +435,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         }
         uint32_t pk[16];
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack_bf16(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
+        for (int jj = 0; jj < 32; jj += 2) pk[jj >> 1] = pack16<kF16>(__uint_as_float(v[ch][jj]), __uint_as_float(v[ch][jj + 1]));
         tmem_st16(my_t1 + ch * 16, pk);
       }
       tmem_st_wait();
@@ -481,7 +481,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
               d[t] = __uint_as_float(v[ch][j0 + jj + t]) * (__uint_as_float(dp[sc & 1][jj + t]) - dl[t]);
             const int ck = sc * 2 + (jj >> 3);                // 16-byte chunk: 8 queries
             *reinterpret_cast<uint4*>(slot + ((ck ^ (row & 7)) << 4)) =
-                make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+                make_uint4(pack16<kF16>(d[0], d[1]), pack16<kF16>(d[2], d[3]), pack16<kF16>(d[4], d[5]), pack16<kF16>(d[6], d[7]));
           }
         }
       }
@@ -599,7 +599,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
   }
 }
 
-// dq[b, s, h, :] = bf16(scale * acc[b, s, h, :]); acc is (B, Sq, Hq, D) fp32 contiguous, dq has its own strides.
+// dq[b, s, h, :] = scale * acc[b, s, h, :] rounded to bf16 (or fp16); acc is (B, Sq, Hq, D) fp32 contiguous, dq has its own strides.
+template <bool kF16>
 __global__ void __launch_bounds__(256) attn_bwd_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
                                                               long long s0, long long s1, long long s2, int seq, int heads, int dim,
                                                               float scale, long long n_vec) {
@@ -613,17 +614,17 @@ __global__ void __launch_bounds__(256) attn_bwd_dq_cast_kernel(const float* __re
     const long long b = t2 / seq;
     const float4 x = __ldcs(reinterpret_cast<const float4*>(acc + e)), y = __ldcs(reinterpret_cast<const float4*>(acc + e) + 1);
     uint4 w;
-    w.x = pack_bf16(x.x * scale, x.y * scale); w.y = pack_bf16(x.z * scale, x.w * scale);
-    w.z = pack_bf16(y.x * scale, y.y * scale); w.w = pack_bf16(y.z * scale, y.w * scale);
+    w.x = pack16<kF16>(x.x * scale, x.y * scale); w.y = pack16<kF16>(x.z * scale, x.w * scale);
+    w.z = pack16<kF16>(y.x * scale, y.y * scale); w.w = pack16<kF16>(y.z * scale, y.w * scale);
     *reinterpret_cast<uint4*>(dq + b * s0 + s * s1 + h * s2 + d) = w;
   }
 }
 
-template <int D>
+template <int D, bool kF16>
 int launch_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
   static_assert(D == 128, "the drain is written for four 32-column chunks");
   constexpr int smem = FusedSmem<D>::kTotal;
-  auto kern = attn_bwd_fused_kernel<D>;
+  auto kern = attn_bwd_fused_kernel<D, kF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
   dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
   kern<<<grid, kThreads, smem, stream>>>(L.tmap_k, L.tmap_v, L.tmap_q, L.tmap_do, L.tmap_dq, L.args);
@@ -642,16 +643,19 @@ extern "C" int kvax_b200_debug_set_phase_buffer(unsigned int* buf) {
 #endif
 
 int launch_attn_bwd_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
-  if (L.head_dim == 128) return launch_fused<128>(L, stream);
+  if (L.head_dim == 128) return L.dtype == KVAX_B200_F16 ? launch_fused<128, true>(L, stream) : launch_fused<128, false>(L, stream);
   return KVAX_B200_EUNSUPPORTED;
 }
 
 int launch_attn_bwd_dq_cast(const float* acc, __nv_bfloat16* dq, const long long* dq_strides, int batch, int seq, int heads,
-                            int dim, float scale, cudaStream_t stream) {
+                            int dim, float scale, int dtype, cudaStream_t stream) {
   const long long n_vec = (long long)batch * seq * heads * dim / 8;
   const long long want = (n_vec + 255) / 256;
   const int blocks = int(want < 148 * 16 ? (want > 0 ? want : 1) : 148 * 16);
-  attn_bwd_dq_cast_kernel<<<blocks, 256, 0, stream>>>(acc, dq, dq_strides[0], dq_strides[1], dq_strides[2], seq, heads, dim, scale, n_vec);
+  if (dtype == KVAX_B200_F16)
+    attn_bwd_dq_cast_kernel<true><<<blocks, 256, 0, stream>>>(acc, dq, dq_strides[0], dq_strides[1], dq_strides[2], seq, heads, dim, scale, n_vec);
+  else
+    attn_bwd_dq_cast_kernel<false><<<blocks, 256, 0, stream>>>(acc, dq, dq_strides[0], dq_strides[1], dq_strides[2], seq, heads, dim, scale, n_vec);
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }
 

@@ -128,7 +128,7 @@ constexpr uint32_t kDescN0 = 8u, kDescN1 = 16u;           // ... in the list of 
 constexpr uint32_t kDescLast1 = 32u;                      // ... whose scores group 1 issues last (else group 0)
 constexpr uint32_t kDescFin0 = 64u, kDescFin1 = 128u;     // entry u is the last one of tile 0 / tile 1
 
-template <int D>
+template <int D, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
@@ -251,8 +251,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);   // Q (K-major) x K (K-major)
-    constexpr uint32_t idesc_o = make_idesc_bf16(kTile, D, 0, 1);       // P (TMEM)    x V (N-major)
+    constexpr uint32_t idesc_s = make_idesc_16(kTile, kTile, 0, 0, kF16);   // Q (K-major) x K (K-major)
+    constexpr uint32_t idesc_o = make_idesc_16(kTile, D, 0, 1, kF16);       // P (TMEM)    x V (N-major)
     const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
     const int cnt0 = __shfl_sync(0xffffffffu, n0, 0), cnt1 = __shfl_sync(0xffffffffu, n1, 0);
     bool ok = true;
@@ -462,7 +462,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch][j]), c, neg_m));       // exp2(-inf) = 0 on masked columns
           const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch][j + 1]), c, neg_m));
           rs4[(j >> 1) & 3] += p0 + p1;
-          pk[j >> 1] = pack_bf16(p0, p1);
+          pk[j >> 1] = pack16<kF16>(p0, p1);
         }
         if (ch == 2) {                          // the first half of P (and the rescaled accumulator) is in TMEM by now
           FPH(3)
@@ -499,10 +499,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 w4;
-              w4.x = pack_bf16(__uint_as_float(o[j + 0]) * inv, __uint_as_float(o[j + 1]) * inv);
-              w4.y = pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-              w4.z = pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-              w4.w = pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+              w4.x = pack16<kF16>(__uint_as_float(o[j + 0]) * inv, __uint_as_float(o[j + 1]) * inv);
+              w4.y = pack16<kF16>(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+              w4.z = pack16<kF16>(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+              w4.w = pack16<kF16>(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
               reinterpret_cast<uint4*>(o_row)[(ch * 32 + j) >> 3] = w4;
             }
           }
@@ -538,24 +538,24 @@ extern "C" int kvax_b200_debug_set_fwd_phase_buffer(unsigned int* buf) {
 }
 #endif
 
-int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream) {
+namespace {
+template <int D, bool kF16>
+int launch_pairs(const FwdLaunch& L, cudaStream_t stream) {
   const FwdArgs& a = L.args;
   dim3 grid(((a.list.n_outer_tiles + 1) / 2) * L.batch * a.q_heads, 1, 1);   // one CTA per pair of query tiles and head
-  cudaError_t err;
-  if (L.head_dim == 128) {
-    constexpr int smem = FwdSmem<128>::kTotal;
-    err = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return KVAX_B200_ELAUNCH;
-    attn_fwd_kernel<128><<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
-  } else if (L.head_dim == 64) {
-    constexpr int smem = FwdSmem<64>::kTotal;
-    err = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return KVAX_B200_ELAUNCH;
-    attn_fwd_kernel<64><<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
-  } else {
-    return KVAX_B200_EUNSUPPORTED;
-  }
+  constexpr int smem = FwdSmem<D>::kTotal;
+  auto kern = attn_fwd_kernel<D, kF16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+}  // namespace
+
+int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream) {
+  const bool f16 = L.dtype == KVAX_B200_F16;
+  if (L.head_dim == 128) return f16 ? launch_pairs<128, true>(L, stream) : launch_pairs<128, false>(L, stream);
+  if (L.head_dim == 64) return f16 ? launch_pairs<64, true>(L, stream) : launch_pairs<64, false>(L, stream);
+  return KVAX_B200_EUNSUPPORTED;
 }
 
 }  // namespace kvx

@@ -66,7 +66,7 @@ struct FwdSmem {
   static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
-template <int D>
+template <int D, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
@@ -165,8 +165,8 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one elected lane issues)
-    constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);   // Q (K-major) x K (K-major)
-    constexpr uint32_t idesc_o = make_idesc_bf16(kTile, D, 0, 1);       // P (TMEM)    x V (N-major)
+    constexpr uint32_t idesc_s = make_idesc_16(kTile, kTile, 0, 0, kF16);   // Q (K-major) x K (K-major)
+    constexpr uint32_t idesc_o = make_idesc_16(kTile, D, 0, 1, kF16);       // P (TMEM)    x V (N-major)
     const uint32_t q_lo = sdesc_lo_sw128(smem_u32(sQ), 16);
     const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
     const int n = __shfl_sync(0xffffffffu, count, 0);
@@ -322,7 +322,7 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const float p0 = fast_exp2(fmaf(__uint_as_float(v[ch][j]), c, neg_m));       // exp2(-inf) = 0 on masked columns
           const float p1 = fast_exp2(fmaf(__uint_as_float(v[ch][j + 1]), c, neg_m));
           rs4[(j >> 1) & 3] += p0 + p1;
-          pk[j >> 1] = pack_bf16(p0, p1);
+          pk[j >> 1] = pack16<kF16>(p0, p1);
         }
         if (ch == 2) {                          // the first half of P (and the rescaled accumulator) is in TMEM by now
           tmem_st_wait();
@@ -380,10 +380,10 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 w;
-            w.x = pack_bf16(o[j + 0], o[j + 1]);
-            w.y = pack_bf16(o[j + 2], o[j + 3]);
-            w.z = pack_bf16(o[j + 4], o[j + 5]);
-            w.w = pack_bf16(o[j + 6], o[j + 7]);
+            w.x = pack16<kF16>(o[j + 0], o[j + 1]);
+            w.y = pack16<kF16>(o[j + 2], o[j + 3]);
+            w.z = pack16<kF16>(o[j + 4], o[j + 5]);
+            w.w = pack16<kF16>(o[j + 6], o[j + 7]);
             reinterpret_cast<uint4*>(o_row)[(ch * 32 + j) >> 3] = w;
           }
         }
@@ -411,24 +411,24 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
 }  // namespace
 
-int launch_attn_fwd_one(const FwdLaunch& L, cudaStream_t stream) {
+namespace {
+template <int D, bool kF16>
+int launch_one(const FwdLaunch& L, cudaStream_t stream) {
   const FwdArgs& a = L.args;
   dim3 grid(a.list.n_outer_tiles * L.batch * a.q_heads, 1, 1);
-  cudaError_t err;
-  if (L.head_dim == 128) {
-    constexpr int smem = FwdSmem<128>::kTotal;
-    err = cudaFuncSetAttribute(attn_fwd_one_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return KVAX_B200_ELAUNCH;
-    attn_fwd_one_kernel<128><<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
-  } else if (L.head_dim == 64) {
-    constexpr int smem = FwdSmem<64>::kTotal;
-    err = cudaFuncSetAttribute(attn_fwd_one_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return KVAX_B200_ELAUNCH;
-    attn_fwd_one_kernel<64><<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
-  } else {
-    return KVAX_B200_EUNSUPPORTED;
-  }
+  constexpr int smem = FwdSmem<D>::kTotal;
+  auto kern = attn_fwd_one_kernel<D, kF16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
+  kern<<<grid, kThreads, smem, stream>>>(L.tmap_q, L.tmap_k, L.tmap_v, a);
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
+}
+}  // namespace
+
+int launch_attn_fwd_one(const FwdLaunch& L, cudaStream_t stream) {
+  const bool f16 = L.dtype == KVAX_B200_F16;
+  if (L.head_dim == 128) return f16 ? launch_one<128, true>(L, stream) : launch_one<128, false>(L, stream);
+  if (L.head_dim == 64) return f16 ? launch_one<64, true>(L, stream) : launch_one<64, false>(L, stream);
+  return KVAX_B200_EUNSUPPORTED;
 }
 
 }  // namespace kvx

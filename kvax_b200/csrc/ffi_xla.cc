@@ -112,15 +112,16 @@ ffi::Error fill_shape(kvax_b200_attn_shape* s, const ffi::AnyBuffer& q, const ff
                       int32_t off_first, int32_t off_second) {
   const auto qd = q.dimensions(), kd = k.dimensions(), vd = v.dimensions();
   if (qd.size() != 4 || kd.size() != 4 || vd.size() != 4) return ffi::Error::InvalidArgument("q, k, v must have rank 4");
-  if (q.element_type() != ffi::BF16 || k.element_type() != ffi::BF16 || v.element_type() != ffi::BF16)
-    return ffi::Error::InvalidArgument("q, k, v must be bf16 (the Python side casts other dtypes)");
+  const bool f16 = q.element_type() == ffi::F16;
+  if ((q.element_type() != ffi::BF16 && !f16) || k.element_type() != q.element_type() || v.element_type() != q.element_type())
+    return ffi::Error::InvalidArgument("q, k, v must all be bf16 or all be fp16 (the Python side casts other dtypes)");
   s->batch = int32_t(qd[0]);
   s->q_len = int32_t(qd[1]);
   s->kv_len = int32_t(kd[1]);
   s->q_heads = int32_t(qd[2]);
   s->kv_heads = int32_t(kd[2]);
   s->head_dim = int32_t(qd[3]);
-  s->dtype = KVAX_B200_BF16;
+  s->dtype = f16 ? KVAX_B200_F16 : KVAX_B200_BF16;
   s->assume_sequential_positions = sequential ? 1 : 0;
   s->scale = scale;
   dense_strides(qd, s->q_strides);

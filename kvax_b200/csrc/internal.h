@@ -39,7 +39,7 @@ struct FwdArgs {
 struct FwdLaunch {
   CUtensorMap tmap_q, tmap_k, tmap_v;
   FwdArgs args;
-  int batch, head_dim;
+  int batch, head_dim, dtype;   // dtype: KVAX_B200_BF16 / KVAX_B200_F16 operands (and outputs)
 };
 // CTAs of two neighbouring query tiles that share their K / V tiles (attn_fwd.cu), or of one query tile (attn_fwd_one.cu).
 int launch_attn_fwd(const FwdLaunch& L, cudaStream_t stream);
@@ -65,24 +65,24 @@ struct BwdArgs {
 struct BwdLaunch {
   CUtensorMap tmap_x1, tmap_x2, tmap_y1, tmap_y2;
   BwdArgs args;
-  int batch, head_dim;
+  int batch, head_dim, dtype;
 };
 int launch_attn_bwd(const BwdLaunch& L, bool kv_outer, cudaStream_t stream);
 // delta = rowsum(O * dO); when `dq_acc` is given, the (B, Sq, Hq, D) fp32 dQ accumulator of the fused
 // backward is zero-filled by the same pass.
 int launch_attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, float* dq_acc,
-                          const long long* strides, int batch, int seq, int heads, int head_dim, cudaStream_t stream);
+                          const long long* strides, int batch, int seq, int heads, int head_dim, int dtype, cudaStream_t stream);
 
 // Fused backward (attn_bwd_fused.cu): K, V, Q, dO tensor maps as for the dK/dV kernel plus the map of the
 // fp32 dQ accumulator (B, Sq, Hq, D), boxes of 32 rows x 32 columns, 128-byte swizzle.
 struct FusedBwdLaunch {
   CUtensorMap tmap_k, tmap_v, tmap_q, tmap_do, tmap_dq;
   BwdArgs args;             // list / mask: the kv-outer ones
-  int batch, head_dim;
+  int batch, head_dim, dtype;
 };
 bool attn_bwd_fused_supports(int head_dim);
 int launch_attn_bwd_fused(const FusedBwdLaunch& L, cudaStream_t stream);
 int launch_attn_bwd_dq_cast(const float* acc, __nv_bfloat16* dq, const long long* dq_strides, int batch, int seq, int heads,
-                            int dim, float scale, cudaStream_t stream);
+                            int dim, float scale, int dtype, cudaStream_t stream);
 
 }  // namespace kvx

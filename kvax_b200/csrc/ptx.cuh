@@ -212,12 +212,12 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Instruction descriptor for kind::f16: bf16 A and B, fp32 accumulator.
-//   bits 4-5 c format (1 = f32), 7-9 a format (1 = bf16), 10-12 b format, 15 a major,
+// Instruction descriptor for kind::f16: A and B both bf16 or both fp16, fp32 accumulator.
+//   bits 4-5 c format (1 = f32), 7-9 a format (0 = f16, 1 = bf16), 10-12 b format, 15 a major,
 //   16 b major (0 = K-major, 1 = MN-major), 17-22 N>>3, 24-28 M>>4.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
-         (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_16(int m, int n, int a_mn_major, int b_mn_major, bool f16) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | (uint32_t(a_mn_major) << 15) |
+         (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor for tiles written by TMA with the 128-byte swizzle:
@@ -344,6 +344,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// two fp32 values rounded to the 16-bit operand type of the kernel (fp16 or bf16), `lo` in the low half
+template <bool kF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  return kF16 ? pack_f16(lo, hi) : pack_bf16(lo, hi);
 }
 
 }  // namespace kvx

@@ -57,6 +57,71 @@ def get_context_parallel_mode() -> str:
     return _cp_mode
 
 
+_FP32_OPERANDS = ("auto", "float16", "bfloat16")
+_fp32_operands = "auto"
+
+
+def set_fp32_operand_dtype(mode: str) -> None:
+    """Which 16-bit type fp32 inputs are rounded to.  "float16": the 10-bit fraction of the tf32 arithmetic the
+    reference uses on fp32 tensors, range up to 65504; "bfloat16": 7-bit fraction, the range of fp32; "auto"
+    (default): float16 when the largest magnitude of query, key and value is at most 2^14 (one device-to-host
+    read per call), else bfloat16."""
+    global _fp32_operands
+    if mode not in _FP32_OPERANDS:
+        raise ValueError(f"unknown operand type {mode!r}; expected one of {_FP32_OPERANDS}")
+    _fp32_operands = mode
+
+
+def get_fp32_operand_dtype() -> str:
+    return _fp32_operands
+
+
+def _fp32_operand_dtype(q, k, v) -> torch.dtype:
+    if _fp32_operands != "auto":
+        return torch.float16 if _fp32_operands == "float16" else torch.bfloat16
+    amax = torch.stack([t.detach().abs().amax() for t in (q, k, v)]).max().item()
+    return torch.float16 if amax <= 16384.0 else torch.bfloat16
+
+
+class _GradScaleBox:
+    """Shared by the casts around one call on fp32 tensors: the power of two the output gradient was multiplied
+    with on its way into fp16, which the input gradients are divided by on their way out."""
+
+    def __init__(self):
+        self.inv = None
+
+
+class _ToOperand(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dtype, box):
+        ctx.box, ctx.in_dtype = box, x.dtype
+        return x.to(dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.to(ctx.in_dtype)
+        if ctx.box.inv is not None:
+            g = g * ctx.box.inv
+        return g, None, None
+
+
+class _FromOperand(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, out, dtype, box):
+        ctx.box, ctx.op_dtype = box, out.dtype
+        return out.to(dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.op_dtype == torch.float16:
+            # largest magnitude -> [1, 2): small gradients keep their bits, nothing overflows; exact (power of two)
+            amax = g.abs().amax().clamp_min(1e-30)
+            s = torch.exp2(-torch.floor(torch.log2(amax)))
+            ctx.box.inv = 1.0 / s
+            g = g * s
+        return g.to(ctx.op_dtype), None, None
+
+
 _HX_TRANSPORTS = ("auto", "peer", "nccl")
 _hx_transport = "auto"
 
@@ -178,7 +243,9 @@ def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, sca
     B, Sq, Hq, D = q.shape
     s.batch, s.q_len, s.kv_len = B, Sq, k.shape[1]
     s.q_heads, s.kv_heads, s.head_dim = Hq, k.shape[2], D
-    s.dtype = 0
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise _lib.KvaxB200Error(f"the kernels take bf16 or fp16 operands of one type, got {q.dtype}, {k.dtype}, {v.dtype}")
+    s.dtype = _lib.DTYPE_F16 if q.dtype == torch.float16 else _lib.DTYPE_BF16
     s.assume_sequential_positions = int(bool(sequential))
     s.scale = float(scale)
     for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
@@ -647,12 +714,16 @@ def flash_attention(
             f"got Dqk={head_dim}, Dv={value.shape[-1]}")
     if query.dtype not in (torch.bfloat16, torch.float16, torch.float32):
         raise _lib.KvaxB200Error(f"unsupported dtype {query.dtype}")
+    # bf16 and fp16 tensors are the kernels' operand types (fp32 accumulation).  fp32 tensors -- the reference feeds
+    # them to tl.dot, i.e. tf32 tensor cores with a 10-bit fraction -- are rounded to fp16, which has the same
+    # fraction, when their largest magnitude allows, else to bf16 (`set_fp32_operand_dtype`); the output and the
+    # gradients come back as fp32, and the incoming output gradient is scaled by a power of two into the fp16 range.
     in_dtype = query.dtype
-    if in_dtype != torch.bfloat16:
-        # The kernels compute on bf16 operands with fp32 accumulation.  fp32 / fp16 inputs are
-        # rounded to bf16 first (the reference feeds fp32 to tl.dot, i.e. tf32 tensor cores);
-        # output and gradients come back in the input dtype.
-        query, key, value = query.to(torch.bfloat16), key.to(torch.bfloat16), value.to(torch.bfloat16)
+    bridge = None
+    if in_dtype == torch.float32:
+        bridge = _GradScaleBox()
+        op_dtype = _fp32_operand_dtype(query, key, value)
+        query, key, value = (_ToOperand.apply(t, op_dtype, bridge) for t in (query, key, value))
     if head_dim in _PADDED_HEAD_DIMS:
         # Zero columns change neither Q K^T nor the first head_dim columns of P V; the output is sliced
         # back below and autograd slices the gradients the same way.
@@ -696,4 +767,4 @@ def flash_attention(
             bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
     if head_dim in _PADDED_HEAD_DIMS:
         out = out[..., :head_dim]
-    return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+    return out if bridge is None else _FromOperand.apply(out, in_dtype, bridge)

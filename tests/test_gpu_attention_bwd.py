@@ -203,9 +203,7 @@ def test_autograd_public_api():
     compare("dv", v.grad.float().cpu().numpy(), rv, rows, max_abs=2e-2 + np.abs(rv).max() / 128)
 
 
-def test_fp32_inputs_tiny_config():
-    """The CPU-runnable configuration (fp32 tensors, D=64, block 64): fp32 inputs go through the
-    bf16 kernels and come back as fp32; compared with the fp32 oracle on the unrounded inputs."""
+def _tiny_fp32_run():
     import kvax_b200 as kv
     inp = _zero_pad_dout(gen.make_inputs(gen.CONFIGS["c1_tiny"], seed=0))
     q, k, v, do = (torch.from_numpy(inp[n]).cuda() for n in ("q", "k", "v", "dout"))
@@ -218,16 +216,93 @@ def test_fp32_inputs_tiny_config():
         masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
         out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
         (out * do).sum().backward()
-    assert out.dtype == torch.float32 and q.grad.dtype == torch.float32
+    assert out.dtype == torch.float32 and q.grad.dtype == torch.float32 and k.grad.dtype == torch.float32
     pp, ss = inp["positions"], inp["segment_ids"]
     ref_o, _ = ao.attention_forward(inp["q"], inp["k"], inp["v"], pp, ss, pp, ss, inp["scale"], dtype=np.float64)
     rq, rk, rv = ao.attention_backward(inp["q"], inp["k"], inp["v"], pp, ss, pp, ss, inp["scale"], inp["dout"])
     rows = (ss != -1)[:, :, None, None]
-    # inputs themselves were rounded to bf16 (relative 2^-9): a wider budget than the bf16-vs-bf16 tests
-    compare("out", out.detach().cpu().numpy(), ref_o, rows, max_abs=3e-2, rel_l2=1e-2)
-    compare("dq", q.grad.cpu().numpy(), rq, rows, max_abs=5e-2, rel_l2=1.5e-2)
-    compare("dk", k.grad.cpu().numpy(), rk, rows, max_abs=5e-2, rel_l2=1.5e-2)
-    compare("dv", v.grad.cpu().numpy(), rv, rows, max_abs=5e-2, rel_l2=1.5e-2)
+    return rows, (out.detach().cpu().numpy(), ref_o), (q.grad.cpu().numpy(), rq), (k.grad.cpu().numpy(), rk), (v.grad.cpu().numpy(), rv)
+
+
+def test_fp32_inputs_tiny_config():
+    """The CPU-runnable configuration (fp32 tensors, D=64, block 64) against the fp64 oracle on the UNROUNDED inputs,
+    at the tolerance of the parity statement: fp32 inputs are computed with fp16 operands (the 10-bit fraction of
+    the tf32 arithmetic the reference uses on them) and fp32 accumulation, and come back as fp32."""
+    import kvax_b200 as kv
+    assert kv.get_fp32_operand_dtype() == "auto"
+    rows, o, dq, dk, dv = _tiny_fp32_run()
+    compare("out", *o, rows)
+    compare("dq", *dq, rows)
+    compare("dk", *dk, rows)
+    compare("dv", *dv, rows)
+
+
+def test_fp32_inputs_bf16_operands():
+    """The same with bf16 operands (what inputs beyond the fp16 range get): the inputs themselves are rounded to
+    8 bits, hence a wider budget than the parity statement's."""
+    import kvax_b200 as kv
+    kv.set_fp32_operand_dtype("bfloat16")
+    try:
+        rows, o, dq, dk, dv = _tiny_fp32_run()
+    finally:
+        kv.set_fp32_operand_dtype("auto")
+    compare("out", *o, rows, max_abs=3e-2, rel_l2=1e-2)
+    compare("dq", *dq, rows, max_abs=5e-2, rel_l2=1.5e-2)
+    compare("dk", *dk, rows, max_abs=5e-2, rel_l2=1.5e-2)
+    compare("dv", *dv, rows, max_abs=5e-2, rel_l2=1.5e-2)
+
+
+def test_fp32_inputs_small_output_gradient():
+    """An output gradient of the size a mean-reduced loss produces (1e-7): it is scaled by a power of two on its way
+    into fp16 and the input gradients are scaled back, so nothing underflows."""
+    import kvax_b200 as kv
+    cfg = gen.small_config(seq=512, batch=1, hq=4, hkv=2, head_dim=64)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=5))
+    q, k, v = (torch.from_numpy(inp[n]).cuda().requires_grad_(True) for n in ("q", "k", "v"))
+    do = torch.from_numpy(inp["dout"]).cuda() * 1e-7
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    mesh = kv.Mesh(("data", "context"), (1, 1))
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        out.backward(do)
+    pp, ss = inp["positions"], inp["segment_ids"]
+    rq, rk, rv = ao.attention_backward(inp["q"], inp["k"], inp["v"], pp, ss, pp, ss, inp["scale"], inp["dout"])
+    rows = (ss != -1)[:, :, None, None]
+    compare("dq * 1e7", q.grad.cpu().numpy() * 1e7, rq, rows)
+    compare("dk * 1e7", k.grad.cpu().numpy() * 1e7, rk, rows)
+    compare("dv * 1e7", v.grad.cpu().numpy() * 1e7, rv, rows)
+
+
+@pytest.mark.parametrize("mode", ["fused", "two_kernel"])
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_fp16_tensors(head_dim, mode):
+    """fp16 tensors run on fp16 operands (the reference's tl.dot on fp16 tiles), not through bf16: compared with the
+    oracle on the fp16-rounded inputs at the tolerance of the parity statement; outputs are fp16."""
+    from kvax_b200.ops.flash_attention import attention_backward, attention_forward, check_status
+    from kvax_b200.ops.mask_creator import build_masks
+    cfg = gen.small_config(seq=1024, hq=4, hkv=2, head_dim=head_dim)
+    inp = _zero_pad_dout(gen.make_inputs(cfg, seed=13))
+    h = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.float16)
+    q, k, v, do = (h(inp[n]).cuda() for n in ("q", "k", "v", "dout"))
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    masks = build_masks(p, s, p, s, [(128, 128, False), (128, 128, False), (128, 128, True)], True)
+    out, lse, st = attention_forward(q, k, v, p, s, p, s, masks[0], (128, 128), inp["scale"])
+    dq, dk, dv, st2 = attention_backward(q, k, v, out, do, lse, p, s, p, s, masks[1], masks[2], (128, 128), inp["scale"], mode=mode)
+    torch.cuda.synchronize()
+    check_status(st, "attn_fwd")
+    check_status(st2, "attn_bwd")
+    assert out.dtype == torch.float16 and dq.dtype == torch.float16
+    r = lambda n: h(inp[n]).float().numpy()
+    pp, ss = inp["positions"], inp["segment_ids"]
+    ref_o, _ = ao.attention_forward(r("q"), r("k"), r("v"), pp, ss, pp, ss, inp["scale"], dtype=np.float64)
+    rq, rk, rv = ao.attention_backward(r("q"), r("k"), r("v"), pp, ss, pp, ss, inp["scale"], r("dout"), dtype=np.float64)
+    rows = (ss != -1)[:, :, None, None]
+    compare("out", out.float().cpu().numpy(), ref_o, rows)
+    compare("dq", dq.float().cpu().numpy(), rq, rows)
+    compare("dk", dk.cpu().numpy(), rk, rows)
+    compare("dv", dv.cpu().numpy(), rv, rows)
 
 
 @pytest.mark.parametrize("head_dim", [16, 32])
