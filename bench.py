@@ -643,9 +643,11 @@ def main():
         return
 
     value = flops_step / (ms_step * 1e-3) / 1e12
-    # mask (2), forward (summaries, lists, order, attention), backward (summaries, lists, order, delta, fused kernel, dQ cast)
-    # [+ token permutes; the head exchange rebuilds the masks]
-    kernels_per_step = 2 + (3 + 1) + (3 + 1 + 1 + 1) + (0 if cp == 1 else (12 if hx else 6))
+    # kernels of this library per step: mask builder (1), forward (tile summaries, lists, order, attention),
+    # backward (tile summaries, lists, order, delta + zero fill, fused kernel, dQ cast); with context parallelism the
+    # head exchange adds the rebuilt masks (1), two token un-permutations and eight exchange kernels (q, k, v, o, do,
+    # dq, dk, dv), the all-gather schedule four token (un-)permutations
+    kernels_per_step = 1 + 4 + 6 + (0 if cp == 1 else (11 if hx else 4))
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": cp, "steps": K, "warmup": W,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

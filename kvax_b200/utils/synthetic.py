@@ -48,6 +48,7 @@ CONFIGS = {
     # a dense causal case small enough for profiler captures (inputs still exceed no cache
     # budget that matters: K+V per head are streamed from L2/HBM)
     "profile_dense_8k": Config("profile_dense_8k", 2, 8192, 16, 16, 128, 128, 8192, 8192, 0.0, 0.0),
+    "profile_dense_16k": Config("profile_dense_16k", 1, 16384, 16, 16, 128, 128, 16384, 16384, 0.0, 0.0),
     # context-parallel Llama-3-70B attention shape
     "c5_cp_128k": Config("c5_cp_128k", 1, 131072, 64, 8, 128, 128, 1024, 65536, 0.0, 0.0),
 }
