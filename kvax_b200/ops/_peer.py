@@ -79,11 +79,15 @@ class PeerArena:
                 self.release()
 
     def release(self) -> None:
+        """Collective: every rank first closes its views of the peers' buffers, then (after a barrier) frees its own --
+        a buffer must not be freed while another process still has it open."""
         lib = _lib.load()
         with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
             for q in self.peers:
                 lib.kvax_b200_peer_buffer_close(q)
             self.peers = []
+            dist.barrier(group=self.group)
             if self.ptr:
                 lib.kvax_b200_peer_buffer_free(self.ptr)
                 self.ptr = None
@@ -108,8 +112,6 @@ def _arena(group, device: torch.device, nbytes: int):
     if a is not None and a.nbytes >= 2 * nbytes:
         return a
     if a is not None:                      # grow: every rank takes this branch together (same sizes everywhere)
-        torch.cuda.synchronize(device)
-        dist.barrier(group=group)
         a.release()
     a = PeerArena(group, device, 2 * _align(nbytes + nbytes // 8))
     _arenas[key] = a if a.ok else False

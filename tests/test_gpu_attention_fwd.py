@@ -66,6 +66,40 @@ def test_forward_small_docmask(head_dim, restart):
     _check(inp, out, lse)
 
 
+def _layout_inputs(lengths, seq, seed, restart=True, hq=2, hkv=1, batch=1):
+    """Hand-made document layout: `lengths` tokens per document, the rest PAD."""
+    cfg = gen.small_config(seq=seq, batch=batch, hq=hq, hkv=hkv, head_dim=128)
+    inp = gen.make_inputs(cfg, seed=seed)
+    pos = np.zeros((batch, seq), np.int32)
+    seg = np.full((batch, seq), -1, np.int32)
+    at = 0
+    for i, n in enumerate(lengths):
+        seg[:, at:at + n] = i
+        pos[:, at:at + n] = np.arange(n) if restart else np.arange(at, at + n)
+        at += n
+    pos[:, at:] = np.arange(seq - at) if restart else np.arange(at, seq)
+    inp["positions"], inp["segment_ids"] = pos, seg
+    return inp
+
+
+@pytest.mark.parametrize("restart", [True, False])
+def test_forward_tile_pairs_with_unequal_lists(restart):
+    """Documents that end on tile boundaries, so that the two query tiles of a pair have nothing in common: pair (2, 3)
+    has tile 2 in the first document (kv tiles 0-2) and tile 3 in the second (kv tile 3 only), pair (4, 5) has a
+    tile of the second document next to an all-PAD tile (empty list), pair (6, 7) is all PAD (both lists empty)."""
+    inp = _layout_inputs([384, 256], seq=1024, seed=23, restart=restart)
+    out, lse = _run_fwd(inp)
+    _check(inp, out, lse)
+
+
+@pytest.mark.parametrize("n_tiles", [1, 3, 5])
+def test_forward_odd_tile_counts(n_tiles):
+    """Sequences with an odd number of query tiles: the last pair has one tile only."""
+    inp = _layout_inputs([128 * n_tiles - 40], seq=128 * n_tiles, seed=29 + n_tiles)
+    out, lse = _run_fwd(inp)
+    _check(inp, out, lse)
+
+
 @pytest.mark.parametrize("blocks", [(64, 64), (128, 64), (64, 128), (256, 128)])
 def test_forward_mask_block_sizes(blocks):
     cfg = gen.small_config(seq=1024, hq=2, hkv=1, head_dim=128, doc_min=40, doc_max=500)
