@@ -100,8 +100,9 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_ms: int = 20):
         self.gpu = gpu_index
+        self.period_ms = int(period_ms)
         self.proc = None
         self.path = None
 
@@ -110,7 +111,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(self.gpu)],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms), "-i", str(self.gpu)],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -321,6 +322,7 @@ def main():
     ap.add_argument("--no-same-gpu-reference", action="store_true",
                     help="skip timing the reference's own Triton kernels on this GPU (single-GPU runs)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--clock-sample-ms", type=int, default=20, help="period of the nvidia-smi clock samples during the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -433,7 +435,7 @@ def main():
         torch.cuda.synchronize()
         if cp > 1:
             dist.barrier()
-        sampler = ClockSampler(local_rank)
+        sampler = ClockSampler(local_rank, args.clock_sample_ms)
         if rank == 0:
             sampler.start()
         torch.cuda.synchronize()
@@ -483,7 +485,7 @@ def main():
 
             if single is not None:
                 cp_check = {("head_exchange" if hx else "all_gather"): check(run_once())}
-            # where a step's time goes on this rank (CUDA events around the phases of the public call, rank 0)
+            # where a step's time goes on every rank (CUDA events around the phases of the public call)
             import importlib
             fa_mod = importlib.import_module("kvax_b200.ops.flash_attention")   # the module, not the function of that name
             fa_mod.enable_phase_timing(True)
@@ -491,6 +493,9 @@ def main():
                 step()
             cp_phases = {k_: v_ / 2 for k_, v_ in fa_mod.phase_times_ms().items()}
             fa_mod.enable_phase_timing(False)
+            all_phases = [None] * cp
+            dist.all_gather_object(all_phases, cp_phases)
+            cp_phases = {k_: [round(p_.get(k_, 0.0), 3) for p_ in all_phases] for k_ in cp_phases}   # one value per rank
             if hx and not args.no_other_schedule:     # the schedule the reference has: K/V all-gather, dK/dV reduce-scatter
                 kv.set_context_parallel_mode("all_gather")
                 for _ in range(2):
@@ -668,7 +673,7 @@ def main():
         line["same_workload_efficiency"] = same_1gpu["ms_per_step"] / (cp * ms_step)
     if cp > 1:
         line["cp_check"] = cp_check
-        line["cp_phases_ms_rank0"] = cp_phases
+        line["cp_phases_ms_per_rank"] = cp_phases
         if per_rank_tiles:
             mean = sum(per_rank_tiles) / len(per_rank_tiles)
             line["all_gather_tiles_per_rank"] = {"unmasked_tile_pairs": per_rank_tiles, "max_over_mean": max(per_rank_tiles) / mean,
