@@ -322,6 +322,9 @@ def main():
     ap.add_argument("--no-same-gpu-reference", action="store_true",
                     help="skip timing the reference's own Triton kernels on this GPU (single-GPU runs)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--positions", default="restart", choices=("restart", "arange"),
+                    help="positions restart at 0 in every document (the benchmark configurations) or are a global arange "
+                         "(the reference's own convention, for which its block bounds are tight)")
     ap.add_argument("--clock-sample-ms", type=int, default=20, help="period of the nvidia-smi clock samples during the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -353,7 +356,7 @@ def main():
     K = args.steps
 
     # ---- synthetic inputs (layout and masks on the host, tensors on the device) -------
-    inp = gen.make_inputs(cfg, seed=0, with_tensors=False)
+    inp = gen.make_inputs(cfg, seed=0, with_tensors=False, restart_positions=(args.positions == "restart"))
     pos_h, seg_h = inp["positions"], inp["segment_ids"]
     scale = inp["scale"]
     B, S, Hq, Hkv, D = cfg.batch, cfg.seq, cfg.hq, cfg.hkv, cfg.head_dim
@@ -517,6 +520,8 @@ def main():
         peaks = measured_peaks()
         if cp == 1:
             masks = kv.create_attention_mask(q_pos, q_seg, kv_pos, kv_seg, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+            # what the reference's kernels visit: the sum of (upper - lower) over the forward mask, in tile pairs
+            reference_visited = int((masks[0].upper_bounds - masks[0].lower_bounds).clamp_min(0).sum().item())
             qd, kd, vd = q.detach(), k.detach(), v.detach()
             out, lse, st, ws_f = attention_forward(qd, kd, vd, q_pos, q_seg, kv_pos, kv_seg, masks[0], (TILE, TILE), scale, stages=3)
             dq, dk, dv, st2, ws_b = attention_backward(qd, kd, vd, out, do, lse, q_pos, q_seg, kv_pos, kv_seg, masks[1], masks[2],
@@ -660,10 +665,13 @@ def main():
         "config": {"workload": cfg.name, "batch": B, "seq_len": S, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D,
                    "tile": TILE, "parallelism": f"cp{cp}" + ((":head_exchange" if hx else ":all_gather") if cp > 1 else ""), "unmasked_tile_pairs": n_tiles,
                    "flops_per_step": flops_step, "cache": "inputs larger than L2 (Q alone exceeds 126 MB)",
-                   "positions": "restart at 0 in every document", "step": "3 block masks + forward + backward"},
+                   "positions": "restart at 0 in every document" if args.positions == "restart" else "global arange",
+                   "step": "3 block masks + forward + backward"},
         "tokens_per_s": B * S / (ms_step * 1e-3),
         "clocks": clocks, "gpu_launches": kernels_per_step * K, "parts_ms": parts,
     }
+    if cp == 1:
+        line["config"]["tile_pairs_in_reference_bounds"] = reference_visited
     if roofline:
         line["roofline"] = roofline
     if cp == 1 and mask_info:
