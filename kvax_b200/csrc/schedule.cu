@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
 // fall on dQ accumulator lines that are still there.  (Sorting single tiles by length instead mixes the documents
 // of a batch: measured 22 GB of DRAM traffic per fused-backward launch on the 32k workload for 3 GB of algorithmic bytes.)
 // Counting sort of the blocks in one CTA; the order among blocks of equal key is not fixed.
-constexpr int kBins = 2048;
+constexpr int kBins = 2048;                // two per thread of order_kernel
 __global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int32_t* order, int32_t* pair_order, int n_outer,
                                                      int batch) {
   __shared__ int hist[kBins];        // rows per key, then the running start of the key's rows
@@ -230,13 +230,34 @@ __global__ void __launch_bounds__(1024) order_kernel(const int32_t* counts, int3
     atomicAdd(&hist2[key], (rows + 1) / 2);
   }
   __syncthreads();
-  // exclusive prefix over descending bins: start[bin] = number of rows in blocks with a larger key
-  if (threadIdx.x == 0) {
-    int run = 0, run2 = 0;
-    for (int bin = kBins - 1; bin >= 0; --bin) {
-      const int c = hist[bin]; hist[bin] = run; run += c;
-      const int c2 = hist2[bin]; hist2[bin] = run2; run2 += c2;
+  // exclusive prefix over descending bins: start[bin] = number of rows in blocks with a larger key.  Thread r takes the
+  // bins kBins - 1 - 2r and kBins - 2 - 2r (two per thread of the 1024), a block-wide scan of the pair sums does the rest.
+  {
+    __shared__ int warp_tot[32], warp_tot2[32];
+    const int r = threadIdx.x, lane = r & 31, w = r >> 5;
+    const int b0 = kBins - 1 - 2 * r, b1 = b0 - 1;
+    const int c0 = hist[b0], c1 = hist[b1], d0 = hist2[b0], d1 = hist2[b1];
+    int inc = c0 + c1, inc2 = d0 + d1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, o), t2 = __shfl_up_sync(0xffffffffu, inc2, o);
+      if (lane >= o) { inc += t; inc2 += t2; }
     }
+    if (lane == 31) { warp_tot[w] = inc; warp_tot2[w] = inc2; }
+    __syncthreads();
+    if (w == 0) {
+      int t = warp_tot[lane], t2 = warp_tot2[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, t, o), u2 = __shfl_up_sync(0xffffffffu, t2, o);
+        if (lane >= o) { t += u; t2 += u2; }
+      }
+      warp_tot[lane] = t; warp_tot2[lane] = t2;            // inclusive totals of the warps
+    }
+    __syncthreads();
+    const int base = (w ? warp_tot[w - 1] : 0) + inc - (c0 + c1), base2 = (w ? warp_tot2[w - 1] : 0) + inc2 - (d0 + d1);
+    hist[b0] = base; hist[b1] = base + c0;
+    hist2[b0] = base2; hist2[b1] = base2 + d0;
   }
   __syncthreads();
   for (int blk = threadIdx.x; blk < n_blocks; blk += blockDim.x) {
