@@ -242,7 +242,12 @@ int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size
  *   two-kernel (KVAX_B200_BWD_TWO_KERNEL in `flags`, and every head_dim the fused kernel does
  *     not cover): a query-outer dQ kernel and a kv-outer dK/dV kernel, seven products per
  *     tile pair, bit-reproducible. */
-enum { KVAX_B200_BWD_TWO_KERNEL = 1 };
+enum {
+  KVAX_B200_BWD_TWO_KERNEL = 1,
+  /* dk and dv point to (B, Skv, Hkv, D) tensors of the operand type (shape.dtype) instead of fp32: for callers
+     that need no fp32 reduction over ranks afterwards; saves the cast pass and half the bytes */
+  KVAX_B200_BWD_DKDV_16BIT = 2
+};
 
 typedef struct kvax_b200_attn_bwd_params {
   kvax_b200_attn_shape shape;
@@ -252,8 +257,8 @@ typedef struct kvax_b200_attn_bwd_params {
   kvax_b200_block_mask mask_dq;        /* one row per query block */
   kvax_b200_block_mask mask_dkdv;      /* one row per kv block    */
   void* dq;                            /* (B, Sq, Hq, D) input dtype, strides = dq_strides */
-  float* dk;                           /* (B, Skv, Hkv, D) fp32 contiguous */
-  float* dv;                           /* (B, Skv, Hkv, D) fp32 contiguous */
+  float* dk;                           /* (B, Skv, Hkv, D) contiguous, fp32 (or see KVAX_B200_BWD_DKDV_16BIT) */
+  float* dv;                           /* (B, Skv, Hkv, D) contiguous, fp32 (or see KVAX_B200_BWD_DKDV_16BIT) */
   int32_t* status;
   /* 0 = everything.  Otherwise a bit set of the parts to launch, for timing or profiling
      one kernel on a workspace a full call has already filled: 1 tile lists, 2 delta (and the

@@ -293,6 +293,7 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   BwdArgs a;
   a.tok = tok; a.lse = p->lse; a.delta = delta;
   a.dq = static_cast<__nv_bfloat16*>(p->dq); a.dq_acc = dq_acc; a.dk = p->dk; a.dv = p->dv; a.status = p->status;
+  a.dkdv_16bit = (p->flags & KVAX_B200_BWD_DKDV_16BIT) ? 1 : 0;
   for (int i = 0; i < 3; ++i) a.dq_strides[i] = dq_strides[i];
   a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;

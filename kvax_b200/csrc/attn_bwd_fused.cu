@@ -132,14 +132,24 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
   const int r = kt * kTile + row;
   const bool is_compute = tid < kComputeThreads;
   const bool row_valid = is_compute && (r < a.tok.kv_len);
-  float* dk_row = a.dk + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
-  float* dv_row = a.dv + (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
+  // dK / dV rows of this thread: fp32, or 16-bit elements of the operand type when the caller asked for that
+  const long long dkv_off = (((long long)b * a.tok.kv_len + r) * a.kv_heads + kvh) * D + half * (D / 2);
+  float* dk_row = a.dk + dkv_off;
+  float* dv_row = a.dv + dkv_off;
+  uint16_t* dk_row16 = reinterpret_cast<uint16_t*>(a.dk) + dkv_off;
+  uint16_t* dv_row16 = reinterpret_cast<uint16_t*>(a.dv) + dkv_off;
 
   if (n_items == 0) {                          // no contributing tile: zero gradients
     if (row_valid) {
-      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.dkdv_16bit) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) { reinterpret_cast<float4*>(dk_row)[i] = z; reinterpret_cast<float4*>(dv_row)[i] = z; }
+        for (int i = 0; i < D / 16; ++i) { reinterpret_cast<uint4*>(dk_row16)[i] = z; reinterpret_cast<uint4*>(dv_row16)[i] = z; }
+      } else {
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { reinterpret_cast<float4*>(dk_row)[i] = z; reinterpret_cast<float4*>(dv_row)[i] = z; }
+      }
     }
     return;
   }
@@ -504,13 +514,30 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         tmem_ld_wait(v1);
         tmem_ld_wait(v2);
         if (row_valid) {
+          if (a.dkdv_16bit) {
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 4) {
-            reinterpret_cast<float4*>(dv_row)[(ch * 32 + jj) >> 2] =
-                make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
-            reinterpret_cast<float4*>(dk_row)[(ch * 32 + jj) >> 2] =
-                make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
-                            __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+            for (int jj = 0; jj < 32; jj += 8) {
+              uint4 w1, w2;
+              w1.x = pack16<kF16>(__uint_as_float(v1[jj + 0]), __uint_as_float(v1[jj + 1]));
+              w1.y = pack16<kF16>(__uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
+              w1.z = pack16<kF16>(__uint_as_float(v1[jj + 4]), __uint_as_float(v1[jj + 5]));
+              w1.w = pack16<kF16>(__uint_as_float(v1[jj + 6]), __uint_as_float(v1[jj + 7]));
+              w2.x = pack16<kF16>(__uint_as_float(v2[jj + 0]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale);
+              w2.y = pack16<kF16>(__uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+              w2.z = pack16<kF16>(__uint_as_float(v2[jj + 4]) * a.scale, __uint_as_float(v2[jj + 5]) * a.scale);
+              w2.w = pack16<kF16>(__uint_as_float(v2[jj + 6]) * a.scale, __uint_as_float(v2[jj + 7]) * a.scale);
+              reinterpret_cast<uint4*>(dv_row16)[(ch * 32 + jj) >> 3] = w1;
+              reinterpret_cast<uint4*>(dk_row16)[(ch * 32 + jj) >> 3] = w2;
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 4) {
+              reinterpret_cast<float4*>(dv_row)[(ch * 32 + jj) >> 2] =
+                  make_float4(__uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]), __uint_as_float(v1[jj + 3]));
+              reinterpret_cast<float4*>(dk_row)[(ch * 32 + jj) >> 2] =
+                  make_float4(__uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
+                              __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+            }
           }
         }
       }

@@ -53,8 +53,9 @@ struct BwdArgs {
   const float* delta;       // (B, Hq, Sq) rowsum(O * dO)
   __nv_bfloat16* dq;        // dQ kernel output, strides dq_strides
   float* dq_acc;            // fused kernel: fp32 dQ accumulator (B, Sq, Hq, D) contiguous, zero on entry
-  float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) fp32 contiguous
+  float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) contiguous: fp32, or (dkdv_16bit) the operand type
   float* dv;
+  int32_t dkdv_16bit;
   int32_t* status;
   long long dq_strides[3];  // element strides (batch, seq, head) of dq
   float scale_log2e, scale;

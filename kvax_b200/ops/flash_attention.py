@@ -291,21 +291,23 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
 
 def attention_backward(q, k, v, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg, mask_dq: AttentionMask,
                        mask_dkdv: AttentionMask, bwd_blocks, scale, assume_sequential_positions=False,
-                       offsets=(0, 0), workspace=None, stages=0, grads=None, mode=None):
+                       offsets=(0, 0), workspace=None, stages=0, grads=None, mode=None, dkdv_in_operand_dtype=False):
     """Direct wrapper of kvax_b200_attn_bwd.  Returns (dq in the input dtype, dk fp32,
     dv fp32, status); dk/dv are summed over the query heads of each kv head.  `mode`:
-    "fused" / "two_kernel" (default: `get_backward_mode()`)."""
+    "fused" / "two_kernel" (default: `get_backward_mode()`).  `dkdv_in_operand_dtype`: dk / dv come out of the
+    kernels in the dtype of q instead of fp32 (no cast pass afterwards; for callers without a reduction over ranks)."""
     lib = _lib.load()
     if grads is None:
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)     # dense, whatever the strides of q
-        dk = torch.empty(k.shape, dtype=torch.float32, device=k.device)
-        dv = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+        kv_grad_dtype = q.dtype if dkdv_in_operand_dtype else torch.float32
+        dk = torch.empty(k.shape, dtype=kv_grad_dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=kv_grad_dtype, device=v.device)
     else:
         dq, dk, dv = grads
     status, status_ptr = status_word(q.device)
     p = _lib.AttnBwdParams()
     p.stages = int(stages)
-    p.flags = _lib.BWD_TWO_KERNEL if (mode or _bwd_mode) == "two_kernel" else 0
+    p.flags = (_lib.BWD_TWO_KERNEL if (mode or _bwd_mode) == "two_kernel" else 0) | (_lib.BWD_DKDV_16BIT if dkdv_in_operand_dtype else 0)
     if out.stride() != dout.stride():
         dout = dout.contiguous()
         out = out.contiguous()
@@ -578,13 +580,16 @@ class _FlashAttention(torch.autograd.Function):
         if query.shape[1] % bq or k_full.shape[1] % bk:
             raise AssertionError("sequence lengths must be divisible by the backward block sizes")
         with _phase("attention_backward"):
+            # without context parallelism nothing is summed over ranks afterwards: dK / dV leave the kernels in the
+            # input dtype
             dq, dk, dv, _ = attention_backward(query, k_full, v_full, out, dout, lse, q_pos, q_seg, kv_pos, kv_seg,
-                                               masks[1], masks[2], (bq, bk), scale, sequential, offsets)
+                                               masks[1], masks[2], (bq, bk), scale, sequential, offsets,
+                                               dkdv_in_operand_dtype=(cp == 1 and kv_dtype == query.dtype))
         if cp > 1:
             with _phase("scatter_dkv"):
                 dk = _scatter_dkv(dk, cp, group, permuted, kv_dtype)
                 dv = _scatter_dkv(dv, cp, group, permuted, kv_dtype)
-        else:
+        elif dk.dtype != kv_dtype:
             dk, dv = dk.to(kv_dtype), dv.to(kv_dtype)
         return (dq, dk, dv) + (None,) * 13
 
@@ -647,7 +652,8 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
             dout_h = _seq_to_heads(dout.contiguous(), cp, group, permuted)
         with _phase("attention_backward"):
             dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
-                                                     masks[1], masks[2], (bq, bk), scale, sequential, (0, 0))
+                                                     masks[1], masks[2], (bq, bk), scale, sequential, (0, 0),
+                                                     dkdv_in_operand_dtype=(kv_dtype == q_h.dtype))
         # every dK / dV element is complete on this rank: cast first, then exchange
         if fast:
             dq, dk, dv = _exchange((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), False, cp, rank, group, permuted)

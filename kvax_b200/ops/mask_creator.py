@@ -32,16 +32,27 @@ def _as_i32(x: torch.Tensor, name: str) -> torch.Tensor:
     return x.to(torch.int32).contiguous()
 
 
+# Everything about a call that only depends on shapes and block sizes (workspace size, sizes and offsets of the output
+# arrays inside the one allocation) is worked out once per shape.
+_layouts: dict[tuple, tuple] = {}
+
+
+def _int32_input(x: torch.Tensor, name: str) -> torch.Tensor:
+    if x.dtype == torch.int32 and x.is_cuda and x.dim() == 2 and x.is_contiguous():
+        return x
+    return _as_i32(x, name)
+
+
 class MaskPlan:
     """One prepared call of kvax_b200_mask_build: argument struct, output arrays and workspace are set up once,
     `launch()` only enqueues the kernel on the current stream (for callers that rebuild masks of the same shape
     into the same arrays every step, and for timing the kernel without host overhead)."""
 
     def __init__(self, query_positions, query_segment_ids, kv_positions, kv_segment_ids, block_specs, skip_pad_tokens=True):
-        qp = _as_i32(query_positions, "query_positions")
-        qs = _as_i32(query_segment_ids, "query_segment_ids")
-        kp = _as_i32(kv_positions, "kv_positions")
-        ks = _as_i32(kv_segment_ids, "kv_segment_ids")
+        qp = _int32_input(query_positions, "query_positions")
+        qs = _int32_input(query_segment_ids, "query_segment_ids")
+        kp = _int32_input(kv_positions, "kv_positions")
+        ks = _int32_input(kv_segment_ids, "kv_segment_ids")
         B, Sq = qp.shape
         Skv = kp.shape[1]
         if qs.shape != (B, Sq) or kp.shape != (B, Skv) or ks.shape != (B, Skv):
@@ -58,22 +69,31 @@ class MaskPlan:
         for i, (bq, bk, kv_outer) in enumerate(block_specs):
             d = p.masks[i]
             d.q_block, d.kv_block, d.kv_outer = int(bq), int(bk), int(bool(kv_outer))
-        self.ws_bytes = self._lib.kvax_b200_mask_workspace_bytes(p)
-        if self.ws_bytes == 0:
-            raise _lib.KvaxB200Error("kvax_b200_mask_workspace_bytes rejected the arguments")
-        # one allocation holds the workspace and every output array (each output starts on a 256-byte boundary)
-        sizes = [(Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq for (bq, bk, kv_outer) in block_specs]
-        out_bytes = [((4 * B * n * 4 + 255) // 256) * 256 for n in sizes]
-        ws_aligned = ((self.ws_bytes + 255) // 256) * 256
-        self._blob = torch.empty(ws_aligned + sum(out_bytes), dtype=torch.uint8, device=qp.device)
-        outs, off = [], ws_aligned
-        for i, n in enumerate(sizes):
-            arrs = self._blob[off:off + 4 * B * n * 4].view(torch.int32).view(4, B, 1, n)
-            off += out_bytes[i]
+        key = (B, Sq, Skv, tuple((int(bq), int(bk), bool(kv)) for bq, bk, kv in block_specs))
+        layout = _layouts.get(key)
+        if layout is None:
+            ws_bytes = self._lib.kvax_b200_mask_workspace_bytes(p)
+            if ws_bytes == 0:
+                raise _lib.KvaxB200Error("kvax_b200_mask_workspace_bytes rejected the arguments")
+            # one int32 allocation holds the workspace and every output array (each output starts on a 256-byte boundary)
+            sizes = [(Skv + bk - 1) // bk if kv_outer else (Sq + bq - 1) // bq for (bq, bk, kv_outer) in block_specs]
+            offs, off = [], ((ws_bytes + 255) // 256) * 64            # in int32 elements
+            for n in sizes:
+                offs.append(off)
+                off += ((4 * B * n * 4 + 255) // 256) * 64
+            layout = _layouts[key] = (ws_bytes, tuple(sizes), tuple(offs), off)
+        self.ws_bytes, sizes, offs, total = layout
+        self._blob = torch.empty(total, dtype=torch.int32, device=qp.device)
+        base = self._blob.data_ptr()
+        masks = []
+        for i, (n, off) in enumerate(zip(sizes, offs)):
+            arrs = self._blob[off:off + 4 * B * n].view(4, B, 1, n).unbind(0)
             d = p.masks[i]
-            d.lower, d.upper, d.lower_full, d.upper_full = (arrs[j].data_ptr() for j in range(4))
-            outs.append(arrs)
-        self.masks = tuple(AttentionMask(a[0], a[1], a[2], a[3]) for a in outs)
+            step = 4 * B * n
+            d.lower, d.upper, d.lower_full, d.upper_full = (base + 4 * off, base + 4 * off + step,
+                                                            base + 4 * off + 2 * step, base + 4 * off + 3 * step)
+            masks.append(AttentionMask(arrs[0], arrs[1], arrs[2], arrs[3]))
+        self.masks = tuple(masks)
 
     def launch(self) -> tuple[AttentionMask, ...]:
         with torch.cuda.device(self.device):
