@@ -22,7 +22,9 @@ Two context-parallel schedules produce the same results:
   single-device problem in natural token order on those heads, and a second all-to-all
   brings the output (and, in the backward pass, dQ/dK/dV) back to sequence sharding.  The
   work per rank is exactly 1/CP of the whole, whatever the mask, and no gradient reduction
-  is needed: every dK/dV element is complete on one rank.  It needs kv_heads % CP == 0.
+  is needed: every dK/dV element is complete on one rank.  It needs kv_heads % CP == 0; with fewer
+  kv heads than ranks (CP a multiple of kv_heads, q_heads % CP == 0) K / V are all-gathered instead, every rank
+  keeps the kv head its query heads read, and dK / dV are reduce-scattered over the ranks that share a head.
 
 `set_context_parallel_mode("auto")` (the default) picks "head_exchange" when the head
 counts allow it.
@@ -605,8 +607,18 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         from kvax_b200.ops.mask_creator import build_masks
 
         rank = torch.distributed.get_rank(group)
-        fast = _fast_exchange_ok(query) and _fast_exchange_ok(key) and _fast_exchange_ok(value)
-        if fast:
+        # Fewer kv heads than ranks (CP a multiple of kv_heads): the query heads are exchanged as usual; a kv head is
+        # then needed, whole, by the CP / kv_heads ranks that hold its query heads.  K and V are small next to Q: they
+        # are all-gathered and every rank keeps the one head its query heads read.
+        shared = cp // key.shape[2] if key.shape[2] % cp else 0         # ranks per kv head, 0: every rank owns kv heads
+        kv_head = rank // shared if shared else 0
+        fast = _fast_exchange_ok(query) and (shared or (_fast_exchange_ok(key) and _fast_exchange_ok(value)))
+        if shared:
+            q_h = _exchange((query,), True, cp, rank, group, permuted)[0] if fast else _seq_to_heads(query, cp, group, permuted)
+            with _phase("gather_kv"):
+                k_h = _gather_kv(key, cp, group, permuted)[:, :, kv_head:kv_head + 1]
+                v_h = _gather_kv(value, cp, group, permuted)[:, :, kv_head:kv_head + 1]
+        elif fast:
             q_h, k_h, v_h = _exchange((query, key, value), True, cp, rank, group, permuted)
         else:
             q_h = _seq_to_heads(query, cp, group, permuted)
@@ -628,7 +640,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         ctx.save_for_backward(q_h, k_h, v_h, out_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
                               *[t for m in masks for t in m.flatten()])
         ctx.n_masks = n_masks
-        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype, rank, fast)
+        ctx.cfg = (scale, bwd_params, sequential, permuted, cp, group, key.dtype, rank, fast, shared, kv_head, key.shape[2])
         if fast:
             return _exchange((out_h,), False, cp, rank, group, permuted)[0]
         return _heads_to_seq(out_h, cp, group, permuted)
@@ -642,7 +654,7 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         if ctx.n_masks != 3:
             raise ValueError("Length of mask_tensors should be equal to two")
         masks = [AttentionMask.unflatten(flat[4 * i:4 * i + 4]) for i in range(3)]
-        scale, bwd_params, sequential, permuted, cp, group, kv_dtype, rank, fast = ctx.cfg
+        scale, bwd_params, sequential, permuted, cp, group, kv_dtype, rank, fast, shared, kv_head, n_kv_heads = ctx.cfg
         bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
         if q_h.shape[1] % bq or k_h.shape[1] % bk:
             raise AssertionError("sequence lengths must be divisible by the backward block sizes")
@@ -653,7 +665,19 @@ class _FlashAttentionHeadExchange(torch.autograd.Function):
         with _phase("attention_backward"):
             dq_h, dk_h, dv_h, _ = attention_backward(q_h, k_h, v_h, out_h, dout_h, lse_h, q_pos_f, q_seg_f, kv_pos, kv_seg,
                                                      masks[1], masks[2], (bq, bk), scale, sequential, (0, 0),
-                                                     dkdv_in_operand_dtype=(kv_dtype == q_h.dtype))
+                                                     dkdv_in_operand_dtype=(not shared and kv_dtype == q_h.dtype))
+        if shared:
+            # the ranks that share a kv head each hold the part of its gradient that comes from their query heads: the
+            # fp32 reduce-scatter of the all-gather schedule sums them (zeros for the heads a rank does not hold)
+            dq = _exchange((dq_h,), False, cp, rank, group, permuted)[0] if fast else _heads_to_seq(dq_h, cp, group, permuted)
+            with _phase("scatter_dkv"):
+                grads = []
+                for part in (dk_h, dv_h):
+                    full = torch.zeros((part.shape[0], part.shape[1], n_kv_heads, part.shape[3]), dtype=torch.float32,
+                                       device=part.device)
+                    full[:, :, kv_head:kv_head + 1] = part
+                    grads.append(_scatter_dkv(full, cp, group, permuted, kv_dtype))
+            return (dq, grads[0], grads[1]) + (None,) * 12
         # every dK / dV element is complete on this rank: cast first, then exchange
         if fast:
             dq, dk, dv = _exchange((dq_h, dk_h.to(kv_dtype), dv_h.to(kv_dtype)), False, cp, rank, group, permuted)
@@ -758,9 +782,12 @@ def flash_attention(
     if tuple(kv_positions.shape) != (B, kv_len) or tuple(kv_segment_ids.shape) != (B, kv_len):
         raise AssertionError("kv positions / segment ids must have shape (batch, kv_seq)")
 
-    can_exchange = cp > 1 and key.shape[2] % cp == 0 and kv_len == Sq * cp
+    n_kv = key.shape[2]
+    heads_fit = n_kv % cp == 0 or (cp % n_kv == 0 and Hq % cp == 0)     # every rank owns kv heads, or shares one
+    can_exchange = cp > 1 and heads_fit and kv_len == Sq * cp
     if _cp_mode == "head_exchange" and cp > 1 and not can_exchange:
-        raise AssertionError("head_exchange context parallelism needs kv_heads % CP == 0 and self-attention lengths")
+        raise AssertionError("head_exchange context parallelism needs kv_heads % CP == 0 (or CP % kv_heads == 0 with "
+                             "q_heads % CP == 0) and self-attention lengths")
     if can_exchange and _cp_mode != "all_gather":
         out = _FlashAttentionHeadExchange.apply(
             query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),

@@ -76,7 +76,8 @@ def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=Tr
             # out and dq come from identical kernels on identical data: exact.  With the
             # all-gather schedule dk/dv are summed over ranks in fp32 in a different order before
             # the bf16 cast; with the head exchange they too are the single-GPU values.
-            exact = name in ("out", "dq") or mode == "head_exchange"
+            # (with fewer kv heads than ranks the head exchange also sums dk / dv over the ranks that share a kv head)
+            exact = name in ("out", "dq") or (mode == "head_exchange" and hkv % world == 0)
             if kv.get_backward_mode() == "fused" and name == "dq":
                 exact = False        # the fused backward sums dQ tiles with fp32 atomics: equal to rounding, not bit for bit
             if exact:
@@ -156,6 +157,9 @@ def main():
     res["fused_hx_docmask_nccl"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=world, pad=0.05,
                                             sequential=False, mode="head_exchange")
     kv.set_head_exchange_transport("auto")
+    # fewer kv heads than ranks: query heads exchanged, K / V gathered, dK / dV reduce-scattered over the sharing ranks
+    res["fused_hx_shared_kv_head"] = run_case(rank, world, dev, seq=1024 * world, batch=1, hq=2 * world, hkv=max(1, world // 2),
+                                              pad=0.05, sequential=False, mode="head_exchange")
     from kvax_b200.ops import _peer
     res["peer_memory_transport"] = "used" if any(a for a in _peer._arenas.values()) else "not available: NCCL transport used"
     kv.set_backward_mode("two_kernel")
