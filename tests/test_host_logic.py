@@ -111,3 +111,42 @@ def test_context_parallel_mode_switch():
     with pytest.raises(ValueError):
         kv.set_context_parallel_mode("ring")
     assert kv.get_context_parallel_mode() == "auto"
+
+
+def test_fp32_bridge_scales_small_output_gradients():
+    """The casts around a call on fp32 tensors: an output gradient far below the fp16 range is multiplied by a power
+    of two on its way in and the input gradients are divided by it on their way out, so a linear map in fp16 gives
+    the fp32 gradient to fp16 precision (no underflow), and exact zeros stay zeros."""
+    from kvax_b200.ops.flash_attention import _FromOperand, _GradScaleBox, _ToOperand
+    torch.manual_seed(0)
+    x = torch.randn(64, 32, requires_grad=True)
+    w = torch.randn(32, 16)
+    box = _GradScaleBox()
+    xo = _ToOperand.apply(x, torch.float16, box)
+    y16 = (xo.float() @ w).to(torch.float16)             # stands in for the fp16 kernels (linear in x)
+    y = _FromOperand.apply(y16, torch.float32, box)
+    assert y.dtype == torch.float32
+    g = torch.randn(64, 16) * 1e-7                       # below the smallest normal fp16 number (6e-5)
+    y.backward(g)
+    ref = g @ w.t()
+    assert x.grad.dtype == torch.float32
+    rel = (x.grad - ref).norm() / ref.norm()
+    assert rel < 2e-3, rel
+    # without the scaling the same gradient would be flushed: every element of g is below half the smallest subnormal?
+    assert float(g.abs().max()) < 6e-5
+    x.grad = None
+    box2 = _GradScaleBox()
+    y2 = _FromOperand.apply(_ToOperand.apply(x, torch.float16, box2) * 1.0, torch.float32, box2)
+    y2.backward(torch.zeros_like(y2))
+    assert float(x.grad.abs().max()) == 0.0
+
+
+def test_fp32_operand_dtype_switch():
+    assert kv.get_fp32_operand_dtype() == "auto"
+    kv.set_fp32_operand_dtype("bfloat16")
+    assert kv.get_fp32_operand_dtype() == "bfloat16"
+    kv.set_fp32_operand_dtype("auto")
+    with pytest.raises(ValueError):
+        kv.set_fp32_operand_dtype("float64")
+    with pytest.raises(ValueError):
+        kv.set_head_exchange_transport("smoke signals")
