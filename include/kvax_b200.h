@@ -218,9 +218,11 @@ typedef struct kvax_b200_attn_fwd_params {
   int32_t flags;                  /* KVAX_B200_FWD_*; 0: the library picks the kernel by sequence length */
 } kvax_b200_attn_fwd_params;
 
-/* Forward kernels: a CTA works on one 128-row query tile, or on two neighbouring ones that
- * share every K / V tile brought on chip.  Same results either way. */
-enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2 };
+/* Forward kernels: a CTA works on one 128-row query tile, or on two work items that share
+ * every K / V tile brought on chip: two neighbouring query tiles of one head, or (grouped-query
+ * attention, an even number of query heads per kv head) one query tile of two query heads of a
+ * kv group.  Same results either way. */
+enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2, KVAX_B200_FWD_HEAD_PAIRS = 4 };
 
 size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p);
 int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,

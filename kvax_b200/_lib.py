@@ -34,7 +34,7 @@ EXPORTS = (
 
 BWD_TWO_KERNEL = 1
 BWD_DKDV_16BIT = 2
-FWD_ONE_TILE, FWD_TILE_PAIRS = 1, 2          # kvax_b200_attn_fwd_params.flags
+FWD_ONE_TILE, FWD_TILE_PAIRS, FWD_HEAD_PAIRS = 1, 2, 4          # kvax_b200_attn_fwd_params.flags
 MAX_PEERS, PEER_HANDLE_BYTES = 16, 64
 DTYPE_BF16, DTYPE_F16 = 0, 1               # kvax_b200_attn_shape.dtype
 

@@ -202,11 +202,16 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.group = s.q_heads / s.kv_heads; a.batch = s.batch;
   L.batch = s.batch; L.head_dim = s.head_dim; L.dtype = s.dtype;
-  // Two query tiles per CTA halve the K / V traffic and pay on long sequences; short ones have too few and too uneven
-  // CTAs that way (measured: 8k tokens 20 % slower, 16k dense 7 % faster, 32k document masks the same).
+  // Two work items per CTA that share their K / V tiles halve the K / V traffic and pay on long sequences; short ones
+  // have too few and too uneven CTAs that way (measured: 8k tokens 20 % slower, 16k dense 7-14 % faster).  With
+  // grouped-query attention the two items are one query tile of two heads of a kv group (identical tile lists), else
+  // two neighbouring query tiles of one head.
   bool pairs = s.kv_len >= 16384;
   if (p->flags & KVAX_B200_FWD_ONE_TILE) pairs = false;
-  if (p->flags & KVAX_B200_FWD_TILE_PAIRS) pairs = true;
+  if (p->flags & (KVAX_B200_FWD_TILE_PAIRS | KVAX_B200_FWD_HEAD_PAIRS)) pairs = true;
+  a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
+  if (p->flags & KVAX_B200_FWD_TILE_PAIRS) a.pair_heads = 0;
+  if ((p->flags & KVAX_B200_FWD_HEAD_PAIRS) && a.group % 2) return KVAX_B200_EUNSUPPORTED;
   return pairs ? launch_attn_fwd(L, st) : launch_attn_fwd_one(L, st);
 }
 

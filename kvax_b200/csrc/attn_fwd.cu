@@ -145,20 +145,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_outer = a.list.n_outer_tiles;
-  int pair_rank, h;
-  decode_block(blockIdx.x, ((n_outer + 1) / 2) * a.batch, a.q_heads, &pair_rank, &h);
-  const long long row0 = __ldg(a.list.pair_order + pair_rank);     // list row of the even tile of the pair
+  // The two work items of the CTA are either two neighbouring query tiles of one head, or -- `pair_heads`, for
+  // grouped-query attention -- one query tile of two query heads that read the same kv head: then both items have
+  // the same tile list, every K / V tile serves both and no union entry is ever one-sided.
+  const int ph = a.pair_heads ? 1 : 0;
+  int pair_rank, hh;
+  decode_block(blockIdx.x, (ph ? n_outer : (n_outer + 1) / 2) * a.batch, ph ? a.q_heads / 2 : a.q_heads, &pair_rank, &hh);
+  const long long row0 = __ldg((ph ? a.list.order : a.list.pair_order) + pair_rank);     // list row of item 0
   const int b = int(row0 / n_outer), qt0 = int(row0 % n_outer);
-  const bool has1 = qt0 + 1 < n_outer;
-  const int kvh = h / a.group;
+  const bool has1 = ph || qt0 + 1 < n_outer;
+  const int h0 = ph ? 2 * hh : hh;                       // query head of item 0; item 1: h0 + ph
+  const int kvh = h0 / a.group;
   const int n0 = __ldg(a.list.counts + row0);
-  const int n1 = has1 ? __ldg(a.list.counts + row0 + 1) : 0;
+  const int n1 = ph ? n0 : (has1 ? __ldg(a.list.counts + row0 + 1) : 0);
   const uint32_t* list0 = a.list.tiles + row0 * a.list.n_inner_tiles;
-  const uint32_t* list1 = list0 + a.list.n_inner_tiles;
+  const uint32_t* list1 = ph ? list0 : list0 + a.list.n_inner_tiles;
 
   const int row = tid & (kTile - 1);
-  const int wg = (tid >> 7) & 1;                         // softmax group = query tile of the pair
-  const int qt = qt0 + wg;
+  const int wg = (tid >> 7) & 1;                         // softmax group = work item of the CTA
+  const int qt = qt0 + (ph ? 0 : wg);
+  const int h = h0 + (ph ? wg : 0);                      // query head of this thread's item
   const int r = qt * kTile + row;                        // query row of a softmax thread
   const bool is_softmax = tid < kSoftmaxThreads;
   const bool row_valid = is_softmax && (r < a.tok.q_len);
@@ -197,7 +203,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_arrive_expect_tx(&bars[B_QFULL0 + g], L::kTileBytes);
 #pragma unroll
         for (int x = 0; x < D / 64; ++x)
-          tma_load_4d(sQ + g * L::kTileBytes + x * L::kBoxBytes, &tmap_q, &bars[B_QFULL0 + g], x * 64, h, (qt0 + g) * kTile, b);
+          tma_load_4d(sQ + g * L::kTileBytes + x * L::kBoxBytes, &tmap_q, &bars[B_QFULL0 + g], x * 64, h0 + (ph ? g : 0),
+                      (qt0 + (ph ? 0 : g)) * kTile, b);
       }
       PairWalk w;
       w.init(list0, n0, list1, n1);
@@ -542,7 +549,8 @@ namespace {
 template <int D, bool kF16>
 int launch_pairs(const FwdLaunch& L, cudaStream_t stream) {
   const FwdArgs& a = L.args;
-  dim3 grid(((a.list.n_outer_tiles + 1) / 2) * L.batch * a.q_heads, 1, 1);   // one CTA per pair of query tiles and head
+  // one CTA per pair of query tiles and head, or per query tile and pair of heads
+  dim3 grid(a.pair_heads ? a.list.n_outer_tiles * L.batch * (a.q_heads / 2) : ((a.list.n_outer_tiles + 1) / 2) * L.batch * a.q_heads, 1, 1);
   constexpr int smem = FwdSmem<D>::kTotal;
   auto kern = attn_fwd_kernel<D, kF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;

@@ -59,15 +59,15 @@ def get_context_parallel_mode() -> str:
     return _cp_mode
 
 
-_FWD_KERNELS = ("auto", "one_tile", "tile_pairs")
+_FWD_KERNELS = ("auto", "one_tile", "tile_pairs", "head_pairs")
 _fwd_kernel = "auto"
 
 
 def set_forward_kernel(kernel: str) -> None:
-    """Which forward kernel runs: a CTA per 128-row query tile ("one_tile"), a CTA per pair of neighbouring query
-    tiles that share their K / V tiles ("tile_pairs": less L2 traffic; ahead on long documents, slightly behind on
-    many short ones), or the library's choice by sequence length ("auto", default: pairs from 16k kv tokens on).
-    Same results to rounding either way."""
+    """Which forward kernel runs: a CTA per 128-row query tile ("one_tile"); a CTA per two work items that share
+    their K / V tiles -- two neighbouring query tiles of one head ("tile_pairs") or one query tile of two query heads
+    of a kv group ("head_pairs", grouped-query attention with an even group); or the library's choice ("auto",
+    default: pairs from 16k kv tokens on, head pairs when the group allows).  Same results to rounding either way."""
     global _fwd_kernel
     if kernel not in _FWD_KERNELS:
         raise ValueError(f"unknown forward kernel {kernel!r}; expected one of {_FWD_KERNELS}")
@@ -292,7 +292,8 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
     status, status_ptr = status_word(q.device)
     p = _lib.AttnFwdParams()
     p.stages = int(stages)
-    p.flags = {"auto": 0, "one_tile": _lib.FWD_ONE_TILE, "tile_pairs": _lib.FWD_TILE_PAIRS}[kernel or _fwd_kernel]
+    p.flags = {"auto": 0, "one_tile": _lib.FWD_ONE_TILE, "tile_pairs": _lib.FWD_TILE_PAIRS,
+               "head_pairs": _lib.FWD_HEAD_PAIRS}[kernel or _fwd_kernel]
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)

@@ -13,9 +13,10 @@ pytestmark = pytest.mark.gpu
 _KERNEL = None
 
 
-@pytest.fixture(autouse=True, params=["one_tile", "tile_pairs"])
+@pytest.fixture(autouse=True, params=["one_tile", "tile_pairs", "head_pairs"])
 def fwd_kernel(request):
-    """Every test of this file runs on both forward kernels (a CTA per query tile / per pair of query tiles)."""
+    """Every test of this file runs on every forward kernel (a CTA per query tile / per pair of query tiles / per
+    pair of query heads of a kv group; the last needs an even number of query heads per kv head)."""
     global _KERNEL
     _KERNEL = request.param
     yield request.param
@@ -29,6 +30,8 @@ def _run_fwd(inp, fwd_blocks=(128, 128), sequential=False, q_slice=None, kv_slic
 
     qs = q_slice or slice(None)
     ks = kv_slice or slice(None)
+    if _KERNEL == "head_pairs" and (inp["q"].shape[2] // inp["k"].shape[2]) % 2:
+        pytest.skip("head pairs need an even number of query heads per kv head")
     q, k, v = to_bf16_cuda(inp["q"][:, qs]), to_bf16_cuda(inp["k"][:, ks]), to_bf16_cuda(inp["v"][:, ks])
     qp, qsg = i32_cuda(inp["positions"][:, qs]), i32_cuda(inp["segment_ids"][:, qs])
     kp, ksg = i32_cuda(inp["positions"][:, ks]), i32_cuda(inp["segment_ids"][:, ks])
