@@ -672,6 +672,9 @@ def main():
     }
     if cp == 1:
         line["config"]["tile_pairs_in_reference_bounds"] = reference_visited
+        # the library's default choice of forward kernel for this shape (see kvax_b200_attn_fwd_params.flags)
+        line["config"]["forward_kernel"] = ("one query tile per CTA" if S < 16384 else
+                                            ("two heads of a kv group per CTA" if (Hq // Hkv) % 2 == 0 else "two query tiles per CTA"))
     if roofline:
         line["roofline"] = roofline
     if cp == 1 and mask_info:
