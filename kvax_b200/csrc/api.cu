@@ -217,22 +217,38 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
 
 namespace {
 
-struct BwdLayout { ListLayout dq, dkdv; SummaryLayout sum; size_t delta_off, acc_off, total; bool fused; };
+struct BwdLayout { ListLayout dq, dkdv; SummaryLayout sum; size_t delta_off, acc_off, kv_acc_off, kv_acc_bytes, total; bool fused; int head_split; };
 
 bool use_fused(const kvax_b200_attn_bwd_params& p) {
   return !(p.flags & KVAX_B200_BWD_TWO_KERNEL) && attn_bwd_fused_supports(p.shape.head_dim);
+}
+
+// Fused backward: CTAs per (kv tile, kv head).  One CTA walks every query head of the kv head; when that gives few CTAs
+// (short sequences, few kv heads: one long CTA then holds up a whole launch) the query heads are divided over 2, 4, ...
+// CTAs whose dK / dV parts are summed in fp32 accumulators.
+int fused_head_split(const kvax_b200_attn_shape& s) {
+  const int group = s.q_heads / s.kv_heads;
+  const long long ctas = (long long)cdiv(s.kv_len, kTile) * s.batch * s.kv_heads;
+  int split = 1;
+#ifndef KVAX_NO_HEAD_SPLIT      // (tuning builds only)
+  while (ctas * split < 16 * 148 && group % (2 * split) == 0) split *= 2;
+#endif
+  return split;
 }
 
 BwdLayout bwd_layout(const kvax_b200_attn_bwd_params& p) {
   const kvax_b200_attn_shape& s = p.shape;
   BwdLayout l;
   l.fused = use_fused(p);
+  l.head_split = l.fused ? fused_head_split(s) : 1;
   l.dq = list_layout(s.batch, s.q_len, s.kv_len, 0);
   l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total);
   l.sum = summary_layout(s.batch, s.q_len, s.kv_len, l.dkdv.total);
   l.delta_off = l.sum.total;
   l.acc_off = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));
-  l.total = l.acc_off + (l.fused ? align256(size_t(s.batch) * s.q_len * s.q_heads * s.head_dim * sizeof(float)) : 0);
+  l.kv_acc_off = l.acc_off + (l.fused ? align256(size_t(s.batch) * s.q_len * s.q_heads * s.head_dim * sizeof(float)) : 0);
+  l.kv_acc_bytes = l.head_split > 1 ? align256(size_t(s.batch) * s.kv_len * s.kv_heads * s.head_dim * sizeof(float)) : 0;
+  l.total = l.kv_acc_off + 2 * l.kv_acc_bytes;      // dK and dV accumulators of the split fused backward
   return l;
 }
 
@@ -261,6 +277,8 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   char* ws = static_cast<char*>(workspace);
   float* delta = reinterpret_cast<float*>(ws + bl.delta_off);
   float* dq_acc = bl.fused ? reinterpret_cast<float*>(ws + bl.acc_off) : nullptr;
+  float* dk_acc = bl.head_split > 1 ? reinterpret_cast<float*>(ws + bl.kv_acc_off) : nullptr;
+  float* dv_acc = bl.head_split > 1 ? reinterpret_cast<float*>(ws + bl.kv_acc_off + bl.kv_acc_bytes) : nullptr;
   const TokenInfo tok = token_info(s);
 
   MaskView mv_dq, mv_dkdv;
@@ -286,6 +304,7 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
     rc = launch_attn_bwd_delta(static_cast<const __nv_bfloat16*>(p->out), static_cast<const __nv_bfloat16*>(p->dout), delta,
                                dq_acc, ostr, s.batch, s.q_len, s.q_heads, s.head_dim, s.dtype, st);
     if (rc) return rc;
+    if (dk_acc && cudaMemsetAsync(dk_acc, 0, 2 * bl.kv_acc_bytes, st) != cudaSuccess) return KVAX_B200_ELAUNCH;
   }
   if (!(stages & (4 | 8 | 16 | 32))) return KVAX_B200_OK;
 
@@ -303,11 +322,16 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
   a.scale = s.scale; a.scale_log2e = s.scale * 1.4426950408889634f;
   a.q_heads = s.q_heads; a.kv_heads = s.kv_heads; a.group = s.q_heads / s.kv_heads;
   a.batch = s.batch;
+  a.head_split = 1; a.dkdv_accumulate = 0;
 
   if (bl.fused) {
     if (stages & 16) {
       FusedBwdLaunch F;
       F.args = a;
+      if (dk_acc) {
+        F.args.head_split = bl.head_split; F.args.dkdv_accumulate = 1; F.args.dkdv_16bit = 0;
+        F.args.dk = dk_acc; F.args.dv = dv_acc;
+      }
       fill_list(&F.args.list, sk);
       F.args.mask = mv_dkdv;
       F.tmap_k = tk; F.tmap_v = tv; F.tmap_q = tq; F.tmap_do = tdo;
@@ -317,8 +341,24 @@ extern "C" int kvax_b200_attn_bwd(const kvax_b200_attn_bwd_params* p, void* work
       rc = launch_attn_bwd_fused(F, st);
       if (rc) return rc;
     }
-    if (stages & 32)
-      return launch_attn_bwd_dq_cast(dq_acc, a.dq, dq_strides, s.batch, s.q_len, s.q_heads, s.head_dim, s.scale, s.dtype, st);
+    if (stages & 32) {
+      rc = launch_attn_bwd_dq_cast(dq_acc, a.dq, dq_strides, s.batch, s.q_len, s.q_heads, s.head_dim, s.scale, s.dtype, st);
+      if (rc) return rc;
+      if (dk_acc) {                 // the summed dK / dV parts go to the caller's arrays: fp32 copy or rounded to the operand type
+        const size_t n = size_t(s.batch) * s.kv_len * s.kv_heads * s.head_dim;
+        if (a.dkdv_16bit) {
+          const long long kstr[3] = {(long long)s.kv_len * s.kv_heads * s.head_dim, (long long)s.kv_heads * s.head_dim, s.head_dim};
+          rc = launch_attn_bwd_dq_cast(dk_acc, reinterpret_cast<__nv_bfloat16*>(p->dk), kstr, s.batch, s.kv_len, s.kv_heads, s.head_dim, 1.f, s.dtype, st);
+          if (rc) return rc;
+          rc = launch_attn_bwd_dq_cast(dv_acc, reinterpret_cast<__nv_bfloat16*>(p->dv), kstr, s.batch, s.kv_len, s.kv_heads, s.head_dim, 1.f, s.dtype, st);
+          if (rc) return rc;
+        } else {
+          if (cudaMemcpyAsync(p->dk, dk_acc, n * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess ||
+              cudaMemcpyAsync(p->dv, dv_acc, n * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+            return KVAX_B200_ELAUNCH;
+        }
+      }
+    }
     return KVAX_B200_OK;
   }
 

@@ -117,11 +117,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int row_rank, kvh;
-  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.kv_heads, &row_rank, &kvh);
+  // With `head_split` > 1 the query heads of a kv head are divided over that many CTAs (short or few lists would
+  // otherwise leave SMs idle behind a few long CTAs); their dK / dV parts meet in fp32 accumulators by atomic adds.
+  int row_rank, hh;
+  decode_block(blockIdx.x, a.list.n_outer_tiles * a.batch, a.kv_heads * a.head_split, &row_rank, &hh);
+  const int kvh = hh / a.head_split;
   const long long list_row = __ldg(a.list.order + row_rank);     // longest lists first
   const int b = int(list_row / a.list.n_outer_tiles), kt = int(list_row % a.list.n_outer_tiles);
-  const int group = a.group;
+  const int group = a.group / a.head_split;                      // query heads of this CTA
+  const int first_head = kvh * a.group + (hh % a.head_split) * group;
   const int count = __ldg(a.list.counts + list_row);
   const uint32_t* list = a.list.tiles + list_row * a.list.n_inner_tiles;
   const int n_items = count * group;           // item i: query head kvh*group + i / count, query tile list[i % count]
@@ -139,8 +143,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
   uint16_t* dk_row16 = reinterpret_cast<uint16_t*>(a.dk) + dkv_off;
   uint16_t* dv_row16 = reinterpret_cast<uint16_t*>(a.dv) + dkv_off;
 
-  if (n_items == 0) {                          // no contributing tile: zero gradients
-    if (row_valid) {
+  if (n_items == 0) {                          // no contributing tile: zero gradients (nothing to add to accumulators)
+    if (row_valid && !a.dkdv_accumulate) {
       if (a.dkdv_16bit) {
         const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -186,7 +190,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     __syncwarp();
     bool ok = true;
     uint32_t e_next = __ldg(list);                 // list entries are fetched one iteration ahead
-    int li = 0, qh = kvh * group;                  // index into the list, query head
+    int li = 0, qh = first_head;                  // index into the list, query head
     PH_BEGIN()
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
@@ -513,7 +517,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         tmem_ld32(tDK + lane_base + half * (D / 2) + ch * 32, v2);
         tmem_ld_wait(v1);
         tmem_ld_wait(v2);
-        if (row_valid) {
+        if (row_valid && a.dkdv_accumulate) {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 4) {
+            red_add_f32x4(dv_row + ch * 32 + jj, __uint_as_float(v1[jj]), __uint_as_float(v1[jj + 1]), __uint_as_float(v1[jj + 2]),
+                          __uint_as_float(v1[jj + 3]));
+            red_add_f32x4(dk_row + ch * 32 + jj, __uint_as_float(v2[jj]) * a.scale, __uint_as_float(v2[jj + 1]) * a.scale,
+                          __uint_as_float(v2[jj + 2]) * a.scale, __uint_as_float(v2[jj + 3]) * a.scale);
+          }
+        } else if (row_valid) {
           if (a.dkdv_16bit) {
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 8) {
@@ -551,7 +563,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     if (lane == 0) prefetch_tmap(&tmap_dq);
     bool ok = true;
     uint32_t e_next = ldg_pinned(list);
-    int li = 0, qh = kvh * group;
+    int li = 0, qh = first_head;
     PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
       const int q0 = int(e_next & ~kPartialBit) * kTile + dw * 32;    // first query row this warp drains
@@ -576,8 +588,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       auto reduce = [&](int ch) {                             // staging buffer ch & 1 -> += accumulator
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && live) {
-          tma_reduce_add_4d(&tmap_dq, stage + (ch & 1) * kStageBuf, ch * 32, yh, q0, b);
+        if (lane == 0) {
+          if (live) tma_reduce_add_4d(&tmap_dq, stage + (ch & 1) * kStageBuf, ch * 32, yh, q0, b);
+          // a group is committed for skipped boxes too (it is empty and complete at once): `buffer_free` counts groups,
+          // and a skipped one must not let the group before it, which may still read the other buffer, fall out of the count
           bulk_commit_group();
         }
       };
@@ -653,7 +667,7 @@ int launch_fused(const FusedBwdLaunch& L, cudaStream_t stream) {
   constexpr int smem = FusedSmem<D>::kTotal;
   auto kern = attn_bwd_fused_kernel<D, kF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return KVAX_B200_ELAUNCH;
-  dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads, 1, 1);
+  dim3 grid(L.args.list.n_outer_tiles * L.batch * L.args.kv_heads * L.args.head_split, 1, 1);
   kern<<<grid, kThreads, smem, stream>>>(L.tmap_k, L.tmap_v, L.tmap_q, L.tmap_do, L.tmap_dq, L.args);
   return cudaGetLastError() == cudaSuccess ? KVAX_B200_OK : KVAX_B200_ELAUNCH;
 }

@@ -57,6 +57,8 @@ struct BwdArgs {
   float* dk;                // dK/dV kernel outputs, (B, Skv, Hkv, D) contiguous: fp32, or (dkdv_16bit) the operand type
   float* dv;
   int32_t dkdv_16bit;
+  int32_t dkdv_accumulate;  // fused kernel: dk / dv are fp32 accumulators (zero on entry) that every CTA adds its part to
+  int32_t head_split;       // fused kernel: CTAs per (kv tile, kv head), each with group / head_split query heads
   int32_t* status;
   long long dq_strides[3];  // element strides (batch, seq, head) of dq
   float scale_log2e, scale;

@@ -78,8 +78,10 @@ def run_case(rank, world, dev, seq, batch, hq, hkv, pad, sequential, permuted=Tr
             # the bf16 cast; with the head exchange they too are the single-GPU values.
             # (with fewer kv heads than ranks the head exchange also sums dk / dv over the ranks that share a kv head)
             exact = name in ("out", "dq") or (mode == "head_exchange" and hkv % world == 0)
-            if kv.get_backward_mode() == "fused" and name == "dq":
-                exact = False        # the fused backward sums dQ tiles with fp32 atomics: equal to rounding, not bit for bit
+            if kv.get_backward_mode() == "fused" and name != "out":
+                # the fused backward sums dQ tiles with fp32 atomics, and on small problems dK / dV parts of several CTAs
+                # too: equal to rounding, not bit for bit
+                exact = False
             if exact:
                 assert err == 0.0, f"{name}: CP differs from single GPU (max {err})"
             else:

@@ -61,16 +61,16 @@ def test_backward_small_docmask(head_dim, hq, hkv, mode):
 
 
 def test_fused_backward_agrees_with_two_kernel_backward():
-    """Same P and dS in both schedules, accumulated in the same order for dK / dV: those are
-    bit-identical.  dQ is summed tile by tile with fp32 atomics in the fused schedule and in
-    TMEM in the other: equal to rounding."""
+    """Same P and dS in both schedules.  dQ is summed tile by tile with fp32 atomics in the fused schedule and in TMEM
+    in the other, and on a problem this small the fused schedule also divides the query heads of a kv head over several
+    CTAs whose dK / dV parts meet in fp32 accumulators: equal to rounding."""
     cfg = gen.small_config(seq=4096, batch=2, hq=8, hkv=2, head_dim=128, doc_min=100, doc_max=3000, pad=0.06)
     inp = _zero_pad_dout(gen.make_inputs(cfg, seed=41))
     _, dq_f, dk_f, dv_f = _run_fwd_bwd(inp, mode="fused")
     _, dq_t, dk_t, dv_t = _run_fwd_bwd(inp, mode="two_kernel")
     rows = (inp["segment_ids"] != -1)[:, :, None, None]
-    np.testing.assert_array_equal(np.where(rows, dk_f, 0), np.where(rows, dk_t, 0))
-    np.testing.assert_array_equal(np.where(rows, dv_f, 0), np.where(rows, dv_t, 0))
+    compare("dk fused vs two-kernel", dk_f, dk_t, rows, max_abs=1e-4 * float(np.abs(dk_t).max()), rel_l2=1e-5)
+    compare("dv fused vs two-kernel", dv_f, dv_t, rows, max_abs=1e-4 * float(np.abs(dv_t).max()), rel_l2=1e-5)
     compare("dq fused vs two-kernel", dq_f, dq_t, rows, max_abs=1e-2 + np.abs(dq_t).max() / 128, rel_l2=4e-3)
 
 
@@ -109,8 +109,9 @@ def test_backward_tiny_config_c1():
 
 
 def test_backward_deterministic():
-    """The two-kernel backward is bit-reproducible; the fused one is for dK and dV (dQ is summed
-    with fp32 atomics)."""
+    """The two-kernel backward is bit-reproducible.  The fused one sums dQ with fp32 atomics, and on small problems
+    like this one (few CTAs: the query heads of a kv head are divided over several CTAs) dK and dV too: equal to
+    rounding from run to run."""
     cfg = gen.small_config(seq=2048, hq=4, hkv=1, head_dim=128)
     inp = _zero_pad_dout(gen.make_inputs(cfg, seed=13))
     a = _run_fwd_bwd(inp, mode="two_kernel")
@@ -119,8 +120,9 @@ def test_backward_deterministic():
         np.testing.assert_array_equal(x, y)
     c = _run_fwd_bwd(inp, mode="fused")
     d = _run_fwd_bwd(inp, mode="fused")
-    for i in (0, 2, 3):
-        np.testing.assert_array_equal(c[i], d[i])
+    np.testing.assert_array_equal(c[0], d[0])
+    for i in (1, 2, 3):
+        np.testing.assert_allclose(c[i], d[i], rtol=0, atol=1e-2 * float(np.abs(c[i]).max()) / 128)
 
 
 @pytest.mark.parametrize("bwd_blocks", [(64, 128), (128, 64)])
