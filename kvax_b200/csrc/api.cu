@@ -230,9 +230,10 @@ int fused_head_split(const kvax_b200_attn_shape& s) {
   const int group = s.q_heads / s.kv_heads;
   const long long ctas = (long long)cdiv(s.kv_len, kTile) * s.batch * s.kv_heads;
   int split = 1;
-#ifndef KVAX_NO_HEAD_SPLIT      // (tuning builds only)
-  while (ctas * split < 16 * 148 && group % (2 * split) == 0) split *= 2;
-#endif
+  // Measured: below 16 CTAs per SM the split pays whatever the group; up to 32 per SM it pays for CTAs that walk eight
+  // or more heads (128k tokens, 32/4 heads: 86.6 -> 82.9 ms) and costs 3 % for four (32k, 32/8 heads: the zero fill
+  // and the final pass over dK / dV outweigh the shorter tail).
+  while (group % (2 * split) == 0 && (ctas * split < 16 * 148 || (ctas * split < 32 * 148 && group / split >= 8))) split *= 2;
   return split;
 }
 
