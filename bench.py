@@ -311,6 +311,8 @@ def main():
                     help="with --gpus N > 1: skip the one-GPU run of the same workload on rank 0")
     ap.add_argument("--cp-mode", default="auto", choices=("auto", "all_gather", "head_exchange"),
                     help="context-parallel schedule for --gpus N > 1")
+    ap.add_argument("--cp-overlap", action="store_true",
+                    help="all-gather schedule: run its collectives under the kernels (own keys first)")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kvax_b200", choices=["kvax_b200", "reference"])
@@ -365,6 +367,7 @@ def main():
     flops_step = 3.5 * flops_fwd
 
     kv.set_context_parallel_mode(args.cp_mode)
+    kv.set_context_parallel_overlap(args.cp_overlap)
     hx = cp > 1 and Hkv % cp == 0 and args.cp_mode != "all_gather"
 
     # ---- N > 1: every rank draws the SAME full tensors (seeded), runs the whole workload alone on its own GPU -- the
@@ -511,6 +514,19 @@ def main():
                 ms_ag = float(t.item())
                 other_schedule = {"parallelism": f"cp{cp}:all_gather", "ms_per_step": ms_ag, "steps": 3,
                                   "value": flops_step / (ms_ag * 1e-3) / 1e12, "unit": UNIT}
+                # the same schedule with its collectives under the kernels: own keys first, gathered keys second
+                kv.set_context_parallel_overlap(True)
+                for _ in range(2):
+                    run_once()
+                if single is not None:
+                    cp_check["all_gather_overlapped"] = check(run_once())
+                ms_ov = cuda_time(step, 3)
+                t = torch.tensor([ms_ov], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms_ov = float(t.item())
+                other_schedule["overlapped"] = {"ms_per_step": ms_ov, "steps": 3, "value": flops_step / (ms_ov * 1e-3) / 1e12,
+                                                "unit": UNIT}
+                kv.set_context_parallel_overlap(args.cp_overlap)
                 kv.set_context_parallel_mode(args.cp_mode)
             single = None
             torch.cuda.empty_cache()

@@ -135,6 +135,15 @@ int kvax_b200_permute_tokens(const void* src, void* dst, int64_t batch, int64_t 
 int kvax_b200_regroup_heads(const void* src, void* dst, int64_t tokens, int32_t cp, int32_t heads_per_group,
                             int64_t head_bytes, int32_t to_groups, kvax_b200_stream_t stream);
 
+/* Merge of two partial attention results over disjoint key sets, for the all-gather schedule of
+ * context parallelism when its collectives overlap the kernels (the reference leaves that overlap
+ * to XLA's asynchronous collectives around the shard_map body, flash_attention_triton.py:2107-2154):
+ * `out_a` / `out_b` are (batch, seq, heads, head_dim) dense outputs of kvax_b200_attn_fwd in `dtype`,
+ * `lse_a` / `lse_b` their (batch, heads, seq) base-2 log-sum-exps (+inf: row without keys).  The merged
+ * output and log-sum-exp replace `out_a` and `lse_a`.  head_dim a multiple of 4, pointers 8-byte aligned. */
+int kvax_b200_attn_merge(void* out_a, float* lse_a, const void* out_b, const float* lse_b, int64_t batch, int64_t seq,
+                         int32_t heads, int32_t head_dim, int32_t dtype, kvax_b200_stream_t stream);
+
 /* Head exchange over peer memory (no counterpart in the reference; it moves the data the
  * reference's all-gather of K / V moves, flash_attention_triton.py:2064-2115, for the
  * head-exchange schedule): one kernel reads a tensor of this GPU and stores every token's heads
@@ -222,7 +231,10 @@ typedef struct kvax_b200_attn_fwd_params {
  * every K / V tile brought on chip: two neighbouring query tiles of one head, or (grouped-query
  * attention, an even number of query heads per kv head) one query tile of two query heads of a
  * kv group.  Same results either way. */
-enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2, KVAX_B200_FWD_HEAD_PAIRS = 4 };
+enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2, KVAX_B200_FWD_HEAD_PAIRS = 4,
+       /* query tiles without any key tile get lse = +inf instead of the reference's 0 (flash_attention_triton.py:253-258),
+          so that kvax_b200_attn_merge can tell them from rows that have keys */
+       KVAX_B200_FWD_EMPTY_LSE_INF = 8 };
 
 size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p);
 int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* workspace, size_t workspace_bytes,

@@ -13,6 +13,7 @@ from kvax_b200.ops import (
     flash_attention,
     get_backward_mode,
     get_context_parallel_mode,
+    get_context_parallel_overlap,
     get_forward_kernel,
     get_fp32_operand_dtype,
     get_head_exchange_transport,
@@ -20,6 +21,7 @@ from kvax_b200.ops import (
     print_mask,
     set_backward_mode,
     set_context_parallel_mode,
+    set_context_parallel_overlap,
     set_forward_kernel,
     set_fp32_operand_dtype,
     set_head_exchange_transport,

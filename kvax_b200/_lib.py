@@ -18,6 +18,7 @@ EXPORTS = (
     "kvax_b200_mask_build_static",
     "kvax_b200_permute_tokens",
     "kvax_b200_regroup_heads",
+    "kvax_b200_attn_merge",
     "kvax_b200_peer_buffer_alloc",
     "kvax_b200_peer_buffer_free",
     "kvax_b200_peer_buffer_export",
@@ -34,7 +35,7 @@ EXPORTS = (
 
 BWD_TWO_KERNEL = 1
 BWD_DKDV_16BIT = 2
-FWD_ONE_TILE, FWD_TILE_PAIRS, FWD_HEAD_PAIRS = 1, 2, 4          # kvax_b200_attn_fwd_params.flags
+FWD_ONE_TILE, FWD_TILE_PAIRS, FWD_HEAD_PAIRS, FWD_EMPTY_LSE_INF = 1, 2, 4, 8          # kvax_b200_attn_fwd_params.flags
 MAX_PEERS, PEER_HANDLE_BYTES = 16, 64
 DTYPE_BF16, DTYPE_F16 = 0, 1               # kvax_b200_attn_shape.dtype
 
@@ -107,6 +108,8 @@ def load() -> C.CDLL:
     lib.kvax_b200_permute_tokens.argtypes = [vp, vp, i64, i64, i64, i32, i32, vp]
     lib.kvax_b200_regroup_heads.restype = C.c_int
     lib.kvax_b200_regroup_heads.argtypes = [vp, vp, i64, i32, i32, i64, i32, vp]
+    lib.kvax_b200_attn_merge.restype = C.c_int
+    lib.kvax_b200_attn_merge.argtypes = [vp, vp, vp, vp, i64, i64, i32, i32, i32, vp]
     lib.kvax_b200_peer_buffer_alloc.restype = C.c_int
     lib.kvax_b200_peer_buffer_alloc.argtypes = [C.c_size_t, C.POINTER(vp)]
     lib.kvax_b200_peer_buffer_free.restype = C.c_int

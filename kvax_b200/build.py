@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libkvax_b200.so")
 SOURCES = ["api.cu", "mask_build.cu", "permute.cu", "schedule.cu", "attn_fwd.cu", "attn_fwd_one.cu", "attn_bwd.cu", "attn_bwd_fused.cu",
-           "wait_probe.cu", "peer_exchange.cu"]
+           "wait_probe.cu", "peer_exchange.cu", "attn_merge.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = [*ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]
 LINK_FLAGS = [*ARCH_FLAGS, "-shared", "-cudart", "static", "-Xcompiler", "-fPIC"]

@@ -209,6 +209,7 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   bool pairs = s.kv_len >= 16384;
   if (p->flags & KVAX_B200_FWD_ONE_TILE) pairs = false;
   if (p->flags & (KVAX_B200_FWD_TILE_PAIRS | KVAX_B200_FWD_HEAD_PAIRS)) pairs = true;
+  a.empty_lse = (p->flags & KVAX_B200_FWD_EMPTY_LSE_INF) ? INFINITY : 0.f;
   a.pair_heads = (a.group % 2 == 0) ? 1 : 0;
   if (p->flags & KVAX_B200_FWD_TILE_PAIRS) a.pair_heads = 0;
   if ((p->flags & KVAX_B200_FWD_HEAD_PAIRS) && a.group % 2) return KVAX_B200_EUNSUPPORTED;

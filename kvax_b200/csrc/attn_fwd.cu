@@ -177,7 +177,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(o_row)[i] = z;
-    *lse_row = 0.f;
+    *lse_row = a.empty_lse;
   }
   if (n0 == 0 && n1 == 0) return;
 

@@ -104,7 +104,7 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int i = 0; i < D / 16; ++i) reinterpret_cast<uint4*>(o_row)[i] = z;
-      if (wg == 0) *lse_row = 0.f;
+      if (wg == 0) *lse_row = a.empty_lse;
     }
     return;
   }

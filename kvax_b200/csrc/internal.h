@@ -34,6 +34,7 @@ struct FwdArgs {
   float scale_log2e;
   int32_t q_heads, group;   // group = Hq / Hkv
   int32_t batch;
+  float empty_lse;          // log-sum-exp written for the rows of query tiles without any key tile (0, or +inf on request)
   int32_t pair_heads;       // pair kernel: a CTA takes one query tile of two heads of a kv group instead of two tiles of one head
 };
 

@@ -16,7 +16,10 @@ Two context-parallel schedules produce the same results:
   all-gathered over NCCL into natural order, the kernels run on the local queries, and the
   backward pass reduce-scatters fp32 dK/dV back to their owners before the cast to the
   input dtype.  Under document masks the work per rank is uneven, because the
-  load-balancing permutation only balances a plain causal mask.
+  load-balancing permutation only balances a plain causal mask.  With
+  `set_context_parallel_overlap(True)` the kernels run on the rank's own keys while the
+  rest is gathered, and the reduce-scatter of the remote keys' gradients runs under the
+  kernels of the local keys.
 * "head_exchange": an all-to-all turns the sequence sharding into a head sharding
   (every rank receives the whole sequence for heads/CP of the heads), the kernels run the
   single-device problem in natural token order on those heads, and a second all-to-all
@@ -57,6 +60,24 @@ def set_context_parallel_mode(mode: str) -> None:
 
 def get_context_parallel_mode() -> str:
     return _cp_mode
+
+
+_cp_overlap = False
+
+
+def set_context_parallel_overlap(on: bool) -> None:
+    """All-gather schedule only: with `on`, the attention kernels first run on the keys and values the rank already
+    holds (its own two chunks, which contain the causal diagonal) while K and V of the other ranks are gathered on a
+    second stream, then on the gathered rest, and the two partial results are merged; in the backward pass the
+    gradients of the remote keys are computed first and their reduce-scatter runs under the kernels of the local
+    keys.  Needs position arrays (not `assume_sequential_positions`) and self-attention lengths; other calls
+    take the serial schedule."""
+    global _cp_overlap
+    _cp_overlap = bool(on)
+
+
+def get_context_parallel_overlap() -> bool:
+    return _cp_overlap
 
 
 _FWD_KERNELS = ("auto", "one_tile", "tile_pairs", "head_pairs")
@@ -281,10 +302,11 @@ def _fill_shape(s: _lib.AttnShape, q, k, v, o, q_pos, q_seg, kv_pos, kv_seg, sca
 
 def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: AttentionMask, fwd_blocks, scale,
                       assume_sequential_positions=False, offsets=(0, 0), workspace=None, stages=0, out=None, lse=None,
-                      kernel=None):
+                      kernel=None, empty_lse_inf=False):
     """Direct wrapper of kvax_b200_attn_fwd.  Returns (out, lse2, status) with lse2 (B, Hq, Sq)
     fp32, the base-2 log-sum-exp of the scaled scores, and the device's status word (a pinned
-    host tensor; see `check_status`).  With `workspace` or `stages` the workspace is returned too."""
+    host tensor; see `check_status`).  With `workspace` or `stages` the workspace is returned too.
+    `empty_lse_inf`: query tiles without any key tile get lse2 = +inf (what `attention_merge` needs) instead of 0."""
     lib = _lib.load()
     B, Sq, Hq, D = q.shape
     out = torch.empty_like(q) if out is None else out
@@ -293,7 +315,7 @@ def attention_forward(q, k, v, q_pos, q_seg, kv_pos, kv_seg, mask_fwd: Attention
     p = _lib.AttnFwdParams()
     p.stages = int(stages)
     p.flags = {"auto": 0, "one_tile": _lib.FWD_ONE_TILE, "tile_pairs": _lib.FWD_TILE_PAIRS,
-               "head_pairs": _lib.FWD_HEAD_PAIRS}[kernel or _fwd_kernel]
+               "head_pairs": _lib.FWD_HEAD_PAIRS}[kernel or _fwd_kernel] | (_lib.FWD_EMPTY_LSE_INF if empty_lse_inf else 0)
     _fill_shape(p.shape, q, k, v, out, q_pos, q_seg, kv_pos, kv_seg, scale, assume_sequential_positions, offsets)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.mask, keep = _block_mask(mask_fwd, *fwd_blocks)
@@ -616,6 +638,184 @@ class _FlashAttention(torch.autograd.Function):
         return (dq, dk, dv) + (None,) * 13
 
 
+def _remote_slots(rank: int, cp: int, permuted: bool) -> list[int]:
+    """Where the chunks a rank does not hold sit in a rank-major all-gather: slot 2 r + h is half h of rank r's local
+    tokens.  Listed in natural (ascending chunk) order, the order the masks need."""
+    slot_of = {_chunk_of(r, h, cp, permuted): 2 * r + h for r in range(cp) for h in (0, 1)}
+    own = {_chunk_of(rank, 0, cp, permuted), _chunk_of(rank, 1, cp, permuted)}
+    return [slot_of[c] for c in range(2 * cp) if c not in own]
+
+
+_slot_index: dict = {}
+
+
+def _slot_index_tensor(rank: int, cp: int, permuted: bool, device) -> torch.Tensor:
+    key = (rank, cp, permuted, str(device))
+    t = _slot_index.get(key)
+    if t is None:
+        t = torch.tensor(_remote_slots(rank, cp, permuted), dtype=torch.long, device=device)
+        _slot_index[key] = t
+    return t
+
+
+def _gather_remote(x: torch.Tensor, gathered: torch.Tensor, cp: int, rank: int, group, permuted: bool) -> torch.Tensor:
+    """All-gather of the local (B, S_loc, ...) slices into `gathered` (cp * B, S_loc, ...), then the chunks of the
+    other ranks in natural order: (B, (cp - 1) * S_loc, ...)."""
+    import torch.distributed as dist
+
+    B, s_loc = x.shape[:2]
+    half = s_loc // 2
+    dist.all_gather_into_tensor(gathered, x, group=group)      # rank-major concatenation
+    idx = _slot_index_tensor(rank, cp, permuted, x.device)
+    g = gathered.view(cp, B, 2, half, *x.shape[2:])
+    if B == 1:
+        rem = g.view(2 * cp, half, *x.shape[2:]).index_select(0, idx)
+        return rem.view(1, (cp - 1) * s_loc, *x.shape[2:])
+    rem = g.transpose(0, 1).reshape(B, 2 * cp, half, *x.shape[2:]).index_select(1, idx)
+    return rem.reshape(B, (cp - 1) * s_loc, *x.shape[2:])
+
+
+def _natural_chunks(x: torch.Tensor, cp: int, chunks: list[int]) -> torch.Tensor:
+    """The given chunks (of 2 cp) of a natural-order per-token array (B, S), concatenated."""
+    B, S = x.shape
+    half = S // (2 * cp)
+    return torch.cat([x[:, c * half:(c + 1) * half] for c in chunks], dim=1).contiguous()
+
+
+def _remote_to_scatter_layout(g_rem: torch.Tensor, cp: int, rank: int, permuted: bool) -> torch.Tensor:
+    """Inverse of the chunk selection of `_gather_remote` for a gradient: (B, (cp - 1) * S_loc, ...) of the remote
+    chunks in natural order -> the reduce-scatter input (cp * B, S_loc, ...), zeros where this rank's own chunks go."""
+    B = g_rem.shape[0]
+    s_loc = g_rem.shape[1] // (cp - 1)
+    half = s_loc // 2
+    tail = tuple(g_rem.shape[2:])
+    idx = _slot_index_tensor(rank, cp, permuted, g_rem.device)
+    if B == 1:
+        out = torch.empty((2 * cp, half) + tail, dtype=g_rem.dtype, device=g_rem.device)
+        out.index_copy_(0, idx, g_rem.view(2 * (cp - 1), half, *tail))
+        out[2 * rank:2 * rank + 2].zero_()
+        return out.view(cp, s_loc, *tail)
+    out = torch.zeros((cp, B, 2, half) + tail, dtype=g_rem.dtype, device=g_rem.device)
+    src = g_rem.view(B, 2 * (cp - 1), half, *tail)
+    for j, slot in enumerate(_remote_slots(rank, cp, permuted)):
+        out[slot // 2, :, slot % 2] = src[:, j]
+    return out.view(cp * B, s_loc, *tail)
+
+
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> torch.cuda.Stream:
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _side_streams[device.index] = s
+    return s
+
+
+def attention_merge(out_a, lse_a, out_b, lse_b):
+    """Direct wrapper of kvax_b200_attn_merge: merges part b into part a (both from `attention_forward` with
+    `empty_lse_inf=True` on the same queries and disjoint keys), in place."""
+    if not (out_a.is_contiguous() and out_b.is_contiguous() and lse_a.is_contiguous() and lse_b.is_contiguous()):
+        raise AssertionError("attention_merge needs dense tensors")
+    B, S, H, D = out_a.shape
+    dtype = _lib.DTYPE_F16 if out_a.dtype == torch.float16 else _lib.DTYPE_BF16
+    with torch.cuda.device(out_a.device):
+        rc = _lib.load().kvax_b200_attn_merge(out_a.data_ptr(), lse_a.data_ptr(), out_b.data_ptr(), lse_b.data_ptr(), B, S, H, D,
+                                              dtype, torch.cuda.current_stream(out_a.device).cuda_stream)
+    _lib.check(rc, "kvax_b200_attn_merge")
+    return out_a, lse_a
+
+
+class _FlashAttentionOverlapped(torch.autograd.Function):
+    """All-gather schedule with its collectives under the kernels (`set_context_parallel_overlap`).  The keys are
+    split into the rank's own two chunks and the chunks of the other ranks; each part is an attention problem of its
+    own (positions and segment ids decide what is allowed, so any subset of the keys in ascending order is a valid
+    kv sequence), with masks built here by the same mask builder; the per-rank masks the caller passed describe the
+    unsplit problem and are not used."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, q_pos, q_seg, kv_pos, kv_seg, n_masks, scale, fwd_params, bwd_params,
+                permuted, cp, rank, group):
+        from kvax_b200.ops.mask_creator import build_masks
+
+        dev = query.device
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        key, value = key.contiguous(), value.contiguous()
+        B, s_loc = key.shape[:2]
+        gathered = [torch.empty((cp * B,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in (key, value)]
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            k_rem = _gather_remote(key, gathered[0], cp, rank, group, permuted)
+            v_rem = _gather_remote(value, gathered[1], cp, rank, group, permuted)
+            k_rem.record_stream(main)
+            v_rem.record_stream(main)
+        own = [_chunk_of(rank, 0, cp, permuted), _chunk_of(rank, 1, cp, permuted)]
+        rest = [c for c in range(2 * cp) if c not in own]
+        kv_pos_own, kv_seg_own = _natural_chunks(kv_pos, cp, own), _natural_chunks(kv_seg, cp, own)
+        kv_pos_rem, kv_seg_rem = _natural_chunks(kv_pos, cp, rest), _natural_chunks(kv_seg, cp, rest)
+        specs = [(fwd_params.query_block_size, fwd_params.kv_block_size, False)]
+        if n_masks == 3:
+            specs.append((bwd_params.kv_block_size, bwd_params.query_block_size, False))
+            specs.append((bwd_params.query_block_size, bwd_params.kv_block_size, True))
+        blocks = (fwd_params.query_block_size, fwd_params.kv_block_size)
+        with _phase("build_masks"):
+            masks_own = build_masks(q_pos, q_seg, kv_pos_own, kv_seg_own, specs, True)
+            masks_rem = build_masks(q_pos, q_seg, kv_pos_rem, kv_seg_rem, specs, True)
+        with _phase("attention_forward_own_keys"):
+            out, lse, _ = attention_forward(query, key, value, q_pos, q_seg, kv_pos_own, kv_seg_own, masks_own[0], blocks, scale,
+                                            empty_lse_inf=True)
+        main.wait_stream(side)
+        del gathered
+        with _phase("attention_forward_remote_keys"):
+            out_r, lse_r, _ = attention_forward(query, k_rem, v_rem, q_pos, q_seg, kv_pos_rem, kv_seg_rem, masks_rem[0], blocks,
+                                                scale, empty_lse_inf=True)
+            attention_merge(out, lse, out_r, lse_r)
+        ctx.save_for_backward(query, key, value, k_rem, v_rem, out, lse, q_pos, q_seg, kv_pos_own, kv_seg_own, kv_pos_rem,
+                              kv_seg_rem, *[t for m in masks_own + masks_rem for t in m.flatten()])
+        ctx.n_masks = n_masks
+        ctx.cfg = (scale, bwd_params, permuted, cp, rank, group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        import torch.distributed as dist
+
+        check_last_status(dout.device)
+        saved = ctx.saved_tensors
+        (query, key, value, k_rem, v_rem, out, lse, q_pos, q_seg, kv_pos_own, kv_seg_own, kv_pos_rem, kv_seg_rem) = saved[:13]
+        flat = saved[13:]
+        if ctx.n_masks != 3:
+            raise ValueError("Length of mask_tensors should be equal to two")
+        masks_own = [AttentionMask.unflatten(flat[4 * i:4 * i + 4]) for i in range(3)]
+        masks_rem = [AttentionMask.unflatten(flat[12 + 4 * i:12 + 4 * i + 4]) for i in range(3)]
+        scale, bwd_params, permuted, cp, rank, group = ctx.cfg
+        bq, bk = bwd_params.query_block_size, bwd_params.kv_block_size
+        if query.shape[1] % bq or key.shape[1] % bk:
+            raise AssertionError("sequence lengths must be divisible by the backward block sizes")
+        dev = query.device
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        dout = dout.contiguous()
+        # remote keys first: their gradients travel while the kernels of the local keys run
+        with _phase("attention_backward_remote_keys"):
+            dq_r, dk_r, dv_r, _ = attention_backward(query, k_rem, v_rem, out, dout, lse, q_pos, q_seg, kv_pos_rem, kv_seg_rem,
+                                                     masks_rem[1], masks_rem[2], (bq, bk), scale)
+            sends = [_remote_to_scatter_layout(g, cp, rank, permuted) for g in (dk_r, dv_r)]
+            landed = [torch.empty((key.shape[0],) + tuple(s.shape[1:]), dtype=s.dtype, device=dev) for s in sends]
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for s, l in zip(sends, landed):
+                dist.reduce_scatter_tensor(l, s, op=dist.ReduceOp.SUM, group=group)
+        with _phase("attention_backward_own_keys"):
+            dq, dk, dv, _ = attention_backward(query, key, value, out, dout, lse, q_pos, q_seg, kv_pos_own, kv_seg_own,
+                                               masks_own[1], masks_own[2], (bq, bk), scale)
+            dq += dq_r
+        main.wait_stream(side)
+        dk = (dk + landed[0]).to(key.dtype)
+        dv = (dv + landed[1]).to(value.dtype)
+        return (dq, dk, dv) + (None,) * 12
+
+
 class _FlashAttentionHeadExchange(torch.autograd.Function):
     """Context parallelism by head exchange (see the module docstring).  The masks of the
     single-device problem are rebuilt from the gathered positions and segment ids with the
@@ -813,6 +1013,12 @@ def flash_attention(
             query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
             _i32(kv_segment_ids), len(mask), float(scale), fwd_params, bwd_params,
             bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, group)
+    elif (cp > 1 and _cp_overlap and not assume_sequential_positions and kv_len == Sq * cp and key.shape[1] == Sq
+          and Sq % 2 == 0 and Sq % max(bwd_params.query_block_size, bwd_params.kv_block_size, fwd_params.kv_block_size) == 0):
+        out = _FlashAttentionOverlapped.apply(
+            query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
+            _i32(kv_segment_ids), len(mask), float(scale), fwd_params, bwd_params,
+            bool(permute_tokens_for_load_balance), cp, rank, group)
     else:
         out = _FlashAttention.apply(
             query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),

@@ -14,8 +14,9 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from kvax_b200.ops.flash_attention import (_exchange_heads_to_seq, _exchange_seq_to_heads, _gather_kv,  # noqa: E402
-                                            _gather_tokens, _heads_to_seq, _scatter_dkv, _seq_to_heads, context_offsets)
+from kvax_b200.ops.flash_attention import (_chunk_of, _exchange_heads_to_seq, _exchange_seq_to_heads, _gather_kv,  # noqa: E402
+                                            _gather_remote, _gather_tokens, _heads_to_seq, _natural_chunks,
+                                            _remote_to_scatter_layout, _scatter_dkv, _seq_to_heads, context_offsets)
 from kvax_b200.utils.sharding import Mesh  # noqa: E402
 from oracle import permutation_oracle as po  # noqa: E402
 
@@ -68,6 +69,23 @@ def main():
                 assert torch.equal(fast2, _seq_to_heads(other, world, None, permuted, permute_fn=oracle_permute))
                 back1, back2 = _exchange_heads_to_seq((fast, fast2), world, rank, None, permuted)
                 assert torch.equal(back1, mineh) and torch.equal(back2, other), f"zero-copy heads->seq mismatch permuted={permuted}"
+            # overlapped all-gather schedule: the chunks of the other ranks in natural order, and the way back of
+            # their gradients (reduce-scatter input with zeros in this rank's own chunks)
+            half = loc // 2
+            own = [_chunk_of(rank, 0, world, permuted), _chunk_of(rank, 1, world, permuted)]
+            rest = [c for c in range(2 * world) if c not in own]
+            landing = torch.empty((world * B, loc, H, D))
+            rem = _gather_remote(mine, landing, world, rank, None, permuted)
+            want = torch.cat([full[:, c * half:(c + 1) * half] for c in rest], dim=1)
+            assert torch.equal(rem, want), f"remote gather mismatch B={B} permuted={permuted}"
+            assert torch.equal(torch.cat([full[:, c * half:(c + 1) * half] for c in own], dim=1), mine)
+            ids = torch.arange(B * S, dtype=torch.int32).view(B, S)
+            assert torch.equal(_natural_chunks(ids, world, rest), torch.cat([ids[:, c * half:(c + 1) * half] for c in rest], dim=1))
+            send = _remote_to_scatter_layout((rank + 1.0) * rem, world, rank, permuted)
+            got_rs = torch.empty((B, loc, H, D))
+            dist.reduce_scatter_tensor(got_rs, send, op=dist.ReduceOp.SUM)
+            expect_rs = sum(r + 1.0 for r in range(world) if r != rank) * mine
+            assert torch.allclose(got_rs, expect_rs), f"remote scatter mismatch B={B} permuted={permuted}"
             tok = torch.arange(B * S, dtype=torch.int32).view(B, S)
             tokg = (oracle_permute(tok.view(B, S, 1, 1), world, False).view(B, S) if permuted else tok)
             gathered = _gather_tokens(tokg[:, rank * loc:(rank + 1) * loc].contiguous(), world, None, permuted, permute_fn=oracle_permute)
