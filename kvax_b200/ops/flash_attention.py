@@ -266,7 +266,6 @@ def _workspace(kind: str, nbytes: int, device: torch.device) -> torch.Tensor:
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 192, 256)   # what the reference accepts
 _KERNEL_HEAD_DIMS = (64, 128)                         # what the sm_100a kernels cover today
-_PADDED_HEAD_DIMS = (16, 32)                          # run as head_dim 64 on zero-padded operands
 
 
 def _i32(x):
@@ -957,11 +956,17 @@ def flash_attention(
         raise ValueError(f"The case with num_mask_tensors={len(mask)} is not supported.")
     if not query.is_cuda:
         raise _lib.KvaxB200Error("flash_attention needs CUDA tensors (there is no CPU fallback)")
-    head_dim = query.shape[-1]
-    if head_dim not in _KERNEL_HEAD_DIMS + _PADDED_HEAD_DIMS or value.shape[-1] != head_dim:
+    head_dim, v_head_dim = query.shape[-1], value.shape[-1]
+    if key.shape[-1] != head_dim:
+        raise AssertionError("query and key must have the same head_dim")
+    if v_head_dim not in _SUPPORTED_HEAD_DIMS:
+        raise AssertionError(f"Attention hid_dim can take values {list(_SUPPORTED_HEAD_DIMS)}")
+    if max(head_dim, v_head_dim) > _KERNEL_HEAD_DIMS[-1]:
         raise _lib.KvaxB200Error(
-            f"the sm_100a kernels cover head_dim in {_KERNEL_HEAD_DIMS + _PADDED_HEAD_DIMS} with Dqk == Dv; "
-            f"got Dqk={head_dim}, Dv={value.shape[-1]}")
+            f"the sm_100a kernels cover head dims up to {_KERNEL_HEAD_DIMS[-1]} (Dqk and Dv may differ); "
+            f"got Dqk={head_dim}, Dv={v_head_dim}")
+    # the kernels run one head_dim for Q K^T and P V: the smallest they have that holds both
+    kernel_dim = next(d for d in _KERNEL_HEAD_DIMS if d >= max(head_dim, v_head_dim))
     if query.dtype not in (torch.bfloat16, torch.float16, torch.float32):
         raise _lib.KvaxB200Error(f"unsupported dtype {query.dtype}")
     # bf16 and fp16 tensors are the kernels' operand types (fp32 accumulation).  fp32 tensors -- the reference feeds
@@ -974,11 +979,12 @@ def flash_attention(
         bridge = _GradScaleBox()
         op_dtype = _fp32_operand_dtype(query, key, value)
         query, key, value = (_ToOperand.apply(t, op_dtype, bridge) for t in (query, key, value))
-    if head_dim in _PADDED_HEAD_DIMS:
-        # Zero columns change neither Q K^T nor the first head_dim columns of P V; the output is sliced
-        # back below and autograd slices the gradients the same way.
-        pad = (0, _KERNEL_HEAD_DIMS[0] - head_dim)
-        query, key, value = (torch.nn.functional.pad(t, pad) for t in (query, key, value))
+    # Zero columns change neither Q K^T nor the first Dv columns of P V; the output is sliced back below and
+    # autograd slices the gradients the same way.
+    if head_dim < kernel_dim:
+        query, key = (torch.nn.functional.pad(t, (0, kernel_dim - head_dim)) for t in (query, key))
+    if v_head_dim < kernel_dim:
+        value = torch.nn.functional.pad(value, (0, kernel_dim - v_head_dim))
     B, Sq, Hq, _ = query.shape
     if key.shape[0] != B or value.shape[:3] != key.shape[:3] or Hq % key.shape[2]:
         raise AssertionError("inconsistent query / key / value shapes")
@@ -1024,6 +1030,6 @@ def flash_attention(
             query, key, value, _i32(query_positions), _i32(query_segment_ids), _i32(kv_positions),
             _i32(kv_segment_ids), tuple(mask), float(scale), fwd_params, bwd_params,
             bool(assume_sequential_positions), bool(permute_tokens_for_load_balance), cp, rank, group)
-    if head_dim in _PADDED_HEAD_DIMS:
-        out = out[..., :head_dim]
+    if v_head_dim < kernel_dim:
+        out = out[..., :v_head_dim]
     return out if bridge is None else _FromOperand.apply(out, in_dtype, bridge)

@@ -329,3 +329,50 @@ def test_small_head_dims_public_api(head_dim):
     compare("dq", q.grad.float().cpu().numpy(), rq, rows, bf16_output=True)
     compare("dk", k.grad.float().cpu().numpy(), rk, rows, bf16_output=True)
     compare("dv", v.grad.float().cpu().numpy(), rv, rows, bf16_output=True)
+
+
+@pytest.mark.parametrize("dqk,dv", [(64, 128), (128, 64), (32, 64), (128, 16)])
+def test_different_qk_and_value_head_dims_public_api(dqk, dv):
+    """Dqk != Dv (the reference's kernels take separate qk_head_dim / value_head_dim,
+    flash_attention_triton.py:173-176): the narrower side is zero-padded to the kernels' head_dim."""
+    import kvax_b200 as kv
+    cfg = gen.small_config(seq=768, batch=1, hq=4, hkv=2, head_dim=dqk)
+    inp = dict(gen.make_inputs(cfg, seed=37))
+    rng = np.random.default_rng(41)
+    inp["v"] = rng.standard_normal(inp["v"].shape[:3] + (dv,)).astype(np.float32)
+    inp["dout"] = rng.standard_normal(inp["q"].shape[:3] + (dv,)).astype(np.float32)
+    inp = _zero_pad_dout(inp)
+    q, k, v, do = (to_bf16_cuda(inp[n]) for n in ("q", "k", "v", "dout"))
+    p, s = i32_cuda(inp["positions"]), i32_cuda(inp["segment_ids"])
+    params = kv.FlashAttentionParamsConfig(128, 128)
+    mesh = kv.Mesh(("data", "context"), (1, 1), rank=0)
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+        masks = kv.create_attention_mask(p, s, p, s, fwd_params=params, bwd_params=params, calc_bwd_mask=True)
+        out = kv.flash_attention(q, k, v, p, s, p, s, masks, scale=inp["scale"], fwd_params=params, bwd_params=params)
+        assert out.shape == q.shape[:3] + (dv,)
+        out.backward(do)
+    assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+    pp, ss = inp["positions"], inp["segment_ids"]
+    ref_o, _ = ao.attention_forward(bf16_round(inp["q"]), bf16_round(inp["k"]), bf16_round(inp["v"]), pp, ss, pp, ss, inp["scale"],
+                                    dtype=np.float32)
+    rq, rk, rv = _oracle_grads(inp)
+    rows = (ss != -1)[:, :, None, None]
+    compare("out", out.detach().float().cpu().numpy(), ref_o, rows, bf16_output=True)
+    compare("dq", q.grad.float().cpu().numpy(), rq, rows, bf16_output=True)
+    compare("dk", k.grad.float().cpu().numpy(), rk, rows, bf16_output=True)
+    compare("dv", v.grad.float().cpu().numpy(), rv, rows, bf16_output=True)
+
+
+def test_wide_head_dims_are_rejected_loudly():
+    """head_dim 192 / 256 are in the reference's list but have no sm_100a kernel here: a clear error, no fallback."""
+    import kvax_b200 as kv
+    from kvax_b200._lib import KvaxB200Error
+    q = torch.zeros(1, 128, 2, 192, dtype=torch.bfloat16, device="cuda")
+    p = torch.arange(128, dtype=torch.int32, device="cuda")[None]
+    s = torch.zeros(1, 128, dtype=torch.int32, device="cuda")
+    mesh = kv.Mesh(("data", "context"), (1, 1), rank=0)
+    with mesh, kv.attention_specs(("data", None, None, None), ("data", None, None, None)):
+        masks = kv.create_attention_mask(p, s, p, s)
+        with pytest.raises(KvaxB200Error, match="head dims up to 128"):
+            kv.flash_attention(q, q, q, p, s, p, s, masks)
