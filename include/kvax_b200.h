@@ -140,7 +140,7 @@ int kvax_b200_regroup_heads(const void* src, void* dst, int64_t tokens, int32_t 
  * to XLA's asynchronous collectives around the shard_map body, flash_attention_triton.py:2107-2154):
  * `out_a` / `out_b` are (batch, seq, heads, head_dim) dense outputs of kvax_b200_attn_fwd in `dtype`,
  * `lse_a` / `lse_b` their (batch, heads, seq) base-2 log-sum-exps (+inf: row without keys).  The merged
- * output and log-sum-exp replace `out_a` and `lse_a`.  head_dim a multiple of 4, pointers 8-byte aligned. */
+ * output and log-sum-exp replace `out_a` and `lse_a`.  head_dim 8, 16, 32, 64, 128 or 256, pointers 16-byte aligned. */
 int kvax_b200_attn_merge(void* out_a, float* lse_a, const void* out_b, const float* lse_b, int64_t batch, int64_t seq,
                          int32_t heads, int32_t head_dim, int32_t dtype, kvax_b200_stream_t stream);
 
