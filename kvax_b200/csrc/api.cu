@@ -92,9 +92,9 @@ int mask_view(const kvax_b200_block_mask& m, bool kv_outer, int q_len, int kv_le
   return KVAX_B200_OK;
 }
 
-struct ListLayout { size_t tiles_off, counts_off, order_off, total; int n_outer, n_inner, batch; };
+struct ListLayout { size_t tiles_off, counts_off, order_off, bitmaps_off, total; int n_outer, n_inner, batch; bool bitmaps; };
 
-ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base) {
+ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base, bool bitmaps = false) {
   ListLayout l;
   l.batch = batch;
   l.n_outer = cdiv(outer_len, kTile); l.n_inner = cdiv(inner_len, kTile);
@@ -102,7 +102,10 @@ ListLayout list_layout(int batch, int outer_len, int inner_len, size_t base) {
   l.counts_off = l.tiles_off + align256(size_t(batch) * l.n_outer * l.n_inner * sizeof(uint32_t));
   l.order_off = l.counts_off + align256(size_t(batch) * l.n_outer * sizeof(int32_t));
   // launch order of the single tiles, then of the pairs of neighbouring tiles (the forward's work items)
-  l.total = l.order_off + align256(size_t(batch) * (l.n_outer + (l.n_outer + 1) / 2) * sizeof(int32_t));
+  l.bitmaps_off = l.order_off + align256(size_t(batch) * (l.n_outer + (l.n_outer + 1) / 2) * sizeof(int32_t));
+  l.bitmaps = bitmaps;
+  // element masks of the first partial entries of every list (attn_common.cuh)
+  l.total = l.bitmaps_off + (bitmaps ? align256(size_t(batch) * l.n_outer * kBitmapSlots * kTile * sizeof(uint4)) : 0);
   return l;
 }
 
@@ -124,12 +127,13 @@ void fill_schedule(ScheduleArgs* sa, const MaskView& mv, const TokenInfo& tok, c
   sa->order = reinterpret_cast<int32_t*>(ws + ll.order_off);
   sa->pair_order = sa->order + size_t(ll.batch) * ll.n_outer;
   sa->inner_summary = inner_summary;
+  sa->bitmaps = ll.bitmaps ? reinterpret_cast<uint4*>(ws + ll.bitmaps_off) : nullptr;
   sa->n_outer_tiles = ll.n_outer; sa->n_inner_tiles = ll.n_inner;
   sa->outer_len = outer_len; sa->inner_len = inner_len;
 }
 
 void fill_list(TileList* l, const ScheduleArgs& sa) {
-  l->tiles = sa.tiles; l->counts = sa.counts; l->order = sa.order; l->pair_order = sa.pair_order;
+  l->tiles = sa.tiles; l->counts = sa.counts; l->order = sa.order; l->pair_order = sa.pair_order; l->bitmaps = sa.bitmaps;
   l->n_outer_tiles = sa.n_outer_tiles; l->n_inner_tiles = sa.n_inner_tiles;
 }
 
@@ -157,7 +161,7 @@ extern "C" const char* kvax_b200_error_string(int code) {
 
 extern "C" size_t kvax_b200_attn_fwd_workspace_bytes(const kvax_b200_attn_fwd_params* p) {
   if (!p || check_shape(p->shape) != KVAX_B200_OK) return 0;
-  const ListLayout ll = list_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, 0);
+  const ListLayout ll = list_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, 0, true);
   return summary_layout(p->shape.batch, p->shape.q_len, p->shape.kv_len, ll.total).total;
 }
 
@@ -167,7 +171,7 @@ extern "C" int kvax_b200_attn_fwd(const kvax_b200_attn_fwd_params* p, void* work
   const kvax_b200_attn_shape& s = p->shape;
   int rc = check_shape(s);
   if (rc) return rc;
-  const ListLayout ll = list_layout(s.batch, s.q_len, s.kv_len, 0);
+  const ListLayout ll = list_layout(s.batch, s.q_len, s.kv_len, 0, true);
   const SummaryLayout sl = summary_layout(s.batch, s.q_len, s.kv_len, ll.total);
   if (!workspace || workspace_bytes < sl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return KVAX_B200_EWORKSPACE;
   if ((s.o_strides[0] | s.o_strides[1] | s.o_strides[2]) & 7 || (reinterpret_cast<uintptr_t>(p->out) & 15)) return KVAX_B200_EUNSUPPORTED;

@@ -10,6 +10,15 @@ namespace kvx {
 
 constexpr int kTile = 128;                 // native tile edge of every attention kernel
 constexpr uint32_t kPartialBit = 0x80000000u;
+// Element masks of partial tiles depend on (batch row, outer tile, inner tile) only, not on the head: the list builder
+// works out the first kBitmapSlots of every list once -- 128 rows x 128 bits, one uint4 per outer row -- and marks
+// those entries; the attention kernels then load 16 bytes per row and tile instead of comparing 128 segment ids and
+// positions per row, tile and head.  Further partial entries of a list are masked by the consumer as before.
+// A marked entry carries its slot: bit 31 partial, bit 30 marked, bits 27-29 the slot, bits 0-26 the inner tile.
+constexpr uint32_t kBitmapBit = 0x40000000u;
+constexpr int kBitmapSlotShift = 27;
+constexpr uint32_t kTileIndexMask = 0x07ffffffu;
+constexpr int kBitmapSlots = 8;
 
 // Block mask plus the geometry needed to read it.
 struct MaskView {
@@ -142,6 +151,7 @@ struct TileList {
   const int32_t* counts;   // (B, n_outer_tiles)
   const int32_t* order;    // (B * n_outer_tiles) launch order: row = b * n_outer_tiles + tile
   const int32_t* pair_order;   // (B * ceil(n_outer_tiles / 2)) launch order of the pairs (2p, 2p+1): row of tile 2p
+  const uint4* bitmaps;        // (B * n_outer_tiles, kBitmapSlots, 128) element masks of marked entries, or null: none marked
   int32_t n_outer_tiles, n_inner_tiles;
 };
 

@@ -104,8 +104,8 @@ struct PairWalk {
   __device__ __forceinline__ bool more() const { return i0 < n0 || i1 < n1; }
   // takes the next union entry: its kv tile and which of the two lists hold it
   __device__ __forceinline__ void next(int* tile, bool* m0, bool* m1) {
-    const uint32_t t0 = (i0 < n0) ? (e0 & ~kPartialBit) : kEnd;
-    const uint32_t t1 = (i1 < n1) ? (e1 & ~kPartialBit) : kEnd;
+    const uint32_t t0 = (i0 < n0) ? (e0 & kTileIndexMask) : kEnd;
+    const uint32_t t1 = (i1 < n1) ? (e1 & kTileIndexMask) : kEnd;
     const uint32_t t = min(t0, t1);
     *tile = int(t); *m0 = (t0 == t); *m1 = (t1 == t);
     if (*m0) { ++i0; if (i0 < n0) e0 = ldg_pinned(l0 + i0); }
@@ -113,8 +113,8 @@ struct PairWalk {
   }
   // membership of the entry after the one `next` returned last (only meaningful while more())
   __device__ __forceinline__ void peek(bool* m0, bool* m1) const {
-    const uint32_t t0 = (i0 < n0) ? (e0 & ~kPartialBit) : kEnd;
-    const uint32_t t1 = (i1 < n1) ? (e1 & ~kPartialBit) : kEnd;
+    const uint32_t t0 = (i0 < n0) ? (e0 & kTileIndexMask) : kEnd;
+    const uint32_t t1 = (i1 < n1) ? (e1 & kTileIndexMask) : kEnd;
     const uint32_t t = min(t0, t1);
     *m0 = (t0 == t); *m1 = (t1 == t);
   }
@@ -392,21 +392,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     constexpr float kLazy = 8.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // element masks of this item's list that the list builder worked out (slot in the entry)
+    const uint4* bitmap_row = a.list.bitmaps + ((row0 + (ph ? 0 : wg)) * kBitmapSlots) * kTile + row;
     uint32_t e_next = (count > 0) ? ldg_pinned(list) : 0u;     // list entries are fetched one iteration ahead
     FPH_BEGIN()
     for (int it = 0; it < count && ok; ++it) {
       const uint32_t e = e_next;
       if (it + 1 < count) e_next = ldg_pinned(list + it + 1);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+      const int c0 = int(e & kTileIndexMask) * kTile;
       const bool partial = (e & kPartialBit) != 0;
 
       // element mask of partial tiles (computed before the scores arrive)
       uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
       if (partial) {
+        if (e & kBitmapBit) {                   // worked out once by the list builder for every head: 16 bytes per row
+          const uint4 w = __ldg(bitmap_row + ((e >> kBitmapSlotShift) & (kBitmapSlots - 1)) * kTile);
+          keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
+        } else {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          keep[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + ch * 32,
-                                        a.tok.sequential ? nullptr : kv_pos + c0 + ch * 32);
+          for (int ch = 0; ch < 4; ++ch)
+            keep[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + ch * 32,
+                                          a.tok.sequential ? nullptr : kv_pos + c0 + ch * 32);
+        }
       }
 
       FPH(0)

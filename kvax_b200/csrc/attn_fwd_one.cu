@@ -135,7 +135,7 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t e_next = __ldg(list);               // list entries are fetched one iteration ahead
       for (int it = 0; it < count && ok; ++it) {
         const int st = it % kKStages, use = it / kKStages;
-        const int u = int(e_next & ~kPartialBit);
+        const int u = int(e_next & kTileIndexMask);
         if (it + 1 < count) e_next = ldg_pinned(list + it + 1);
         if (use > 0) ok = mbar_wait(&bars[B_KEMPTY0 + st], (use - 1) & 1, abort_flag, a.status, B_KEMPTY0 + st);
         if (!ok) break;
@@ -153,7 +153,7 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint32_t e_next = __ldg(list);
       for (int it = 0; it < count && ok; ++it) {
         const int st = it % kVStages, use = it / kVStages;
-        const int u = int(e_next & ~kPartialBit);
+        const int u = int(e_next & kTileIndexMask);
         if (it + 1 < count) e_next = ldg_pinned(list + it + 1);
         if (use > 0) ok = mbar_wait(&bars[B_VEMPTY0 + st], (use - 1) & 1, abort_flag, a.status, B_VEMPTY0 + st);
         if (!ok) break;
@@ -248,20 +248,27 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr float kLazy = 8.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // element masks of this list that the list builder worked out (slot in the entry)
+    const uint4* bitmap_row = a.list.bitmaps + (list_row * kBitmapSlots) * kTile + row;
     uint32_t e_next = (wg < count) ? __ldg(list + wg) : 0u;   // list entries are fetched one iteration ahead
     for (int it = wg; it < count && ok; it += 2) {
       const uint32_t e = e_next;
       if (it + 2 < count) e_next = ldg_pinned(list + it + 2);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+      const int c0 = int(e & kTileIndexMask) * kTile;
       const bool partial = (e & kPartialBit) != 0;
 
       // element mask of partial tiles (computed before the scores arrive)
       uint32_t keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
       if (partial) {
+        if (e & kBitmapBit) {                   // worked out once by the list builder for every head: 16 bytes per row
+          const uint4 w = __ldg(bitmap_row + ((e >> kBitmapSlotShift) & (kBitmapSlots - 1)) * kTile);
+          keep[0] = w.x; keep[1] = w.y; keep[2] = w.z; keep[3] = w.w;
+        } else {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          keep[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + ch * 32,
-                                        a.tok.sequential ? nullptr : kv_pos + c0 + ch * 32);
+          for (int ch = 0; ch < 4; ++ch)
+            keep[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.tok.kv_len, row_valid, q_seg, q_pos, kv_seg + c0 + ch * 32,
+                                          a.tok.sequential ? nullptr : kv_pos + c0 + ch * 32);
+        }
       }
       ok = mbar_wait(&bars[B_SFULL0 + wg], (it >> 1) & 1, abort_flag, a.status, B_SFULL0 + wg);
       if (!ok) break;

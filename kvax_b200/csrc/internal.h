@@ -17,6 +17,7 @@ struct ScheduleArgs {
   int32_t* order;      // (B * n_outer_tiles) launch order of the rows (blocks of neighbours, longest lists first)
   int32_t* pair_order; // (B * ceil(n_outer_tiles / 2)) the same order for pairs (2p, 2p+1): row of the even tile
   const int4* inner_summary;  // (B, n_inner_tiles) {seg_min, seg_max, pos_min, pos_max}
+  uint4* bitmaps;      // (B * n_outer_tiles, kBitmapSlots, 128) element masks of the first partial entries of a list, or null
   int32_t n_outer_tiles, n_inner_tiles;
   int32_t outer_len, inner_len;
 };

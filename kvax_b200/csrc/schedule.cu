@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
   __shared__ int s_red2[4];
   __shared__ unsigned char s_code[kChunk];    // 0 drop, 1 unmasked, 2 needs the exact test, 3 partial
   __shared__ int s_count;
+  __shared__ int s_partial;                   // partial entries of the list so far
+  __shared__ int s_slot_tile[kBitmapSlots];   // inner tile of the partial entry that got bitmap slot i
   const int t = threadIdx.x;
   const int ot = blockIdx.x, b = blockIdx.y;
   const int o = ot * kTile + t;                       // outer token of this thread
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
   vis_hi = min(vis_hi, a.n_inner_tiles * kTile);
 
   uint32_t* out = a.tiles + ((long long)b * a.n_outer_tiles + ot) * a.n_inner_tiles;
-  if (t == 0) s_count = 0;
+  if (t == 0) { s_count = 0; s_partial = 0; }
   __syncthreads();
   if (vis_hi > vis_lo) {
     const int it0 = max(vis_lo, 0) / kTile;
@@ -180,19 +182,46 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
         if (t == 0) s_code[k] = any ? 3 : 0;
       }
       __syncthreads();
-      // C: ordered compaction by warp 0
+      // C: ordered compaction by warp 0.  The first kBitmapSlots partial entries of a query-outer list get an element
+      // mask of their own (step D) and are marked.
+      const bool with_bitmaps = !kKvOuter && a.bitmaps != nullptr;
+      const int partial_before = s_partial;
       if (t < 32) {
-        int cnt = s_count;
+        int cnt = s_count, pcnt = partial_before;
         for (int k0 = 0; k0 < n; k0 += 32) {
           const int k = k0 + t;
           const unsigned char code = (k < n) ? s_code[k] : 0;
           const unsigned m = __ballot_sync(0xffffffffu, code != 0);
-          if (code != 0) out[cnt + __popc(m & ((1u << t) - 1))] = uint32_t(base + k) | (code == 3 ? kPartialBit : 0u);
+          const unsigned pm = __ballot_sync(0xffffffffu, code == 3);
+          if (code != 0) {
+            uint32_t e = uint32_t(base + k) | (code == 3 ? kPartialBit : 0u);
+            const int slot = pcnt + __popc(pm & ((1u << t) - 1));
+            if (code == 3 && with_bitmaps && slot < kBitmapSlots) { e |= kBitmapBit | (uint32_t(slot) << kBitmapSlotShift); s_slot_tile[slot] = base + k; }
+            out[cnt + __popc(m & ((1u << t) - 1))] = e;
+          }
           cnt += __popc(m);
+          pcnt += __popc(pm);
         }
-        if (t == 0) s_count = cnt;
+        if (t == 0) { s_count = cnt; s_partial = pcnt; }
       }
       __syncthreads();
+      // D: element masks of the entries marked in this pass: thread t = outer row t, the very function the consumers
+      // would call on the same arguments
+      if (with_bitmaps) {
+        const int slot_end = min(s_partial, kBitmapSlots);
+        const int32_t* inner_seg = a.tok.kv_seg + (long long)b * a.tok.kv_len;
+        const int32_t* inner_pos = a.tok.sequential ? nullptr : a.tok.kv_pos + (long long)b * a.tok.kv_len;
+        for (int slot = partial_before; slot < slot_end; ++slot) {
+          const int c0 = s_slot_tile[slot] * kTile;
+          uint32_t w[4];
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+            w[ch] = keep_bits32<false>(rb, c0 + ch * 32, a.inner_len, row_valid, o_seg, o_pos, inner_seg + c0 + ch * 32,
+                                       inner_pos ? inner_pos + c0 + ch * 32 : nullptr);
+          a.bitmaps[(((long long)b * a.n_outer_tiles + ot) * kBitmapSlots + slot) * kTile + t] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        __syncthreads();                        // s_slot_tile is reused by the next pass
+      }
     }
   }
   if (t == 0) a.counts[(long long)b * a.n_outer_tiles + ot] = s_count;

@@ -95,6 +95,24 @@ def test_forward_tile_pairs_with_unequal_lists(restart):
     _check(inp, out, lse)
 
 
+@pytest.mark.parametrize("seq,hq,hkv", [(2048, 2, 1), (2048 + 70, 4, 1)])
+def test_forward_many_partial_tiles(seq, hq, hkv):
+    """Segments interleaved in runs of 48 tokens (ids cycling through three values) with global positions: every kv tile
+    up to the diagonal holds keys of the query's segment and others, so every list entry is a partial tile -- up to 17
+    per list.  The first eight take the element masks the list builder worked out, the rest are masked in the
+    attention kernel: both must agree with the oracle."""
+    cfg = gen.small_config(seq=seq, batch=2, hq=hq, hkv=hkv, head_dim=128)
+    inp = gen.make_inputs(cfg, seed=43)
+    idx = np.arange(seq)
+    seg = np.broadcast_to(((idx // 48) % 3).astype(np.int32), (2, seq)).copy()
+    seg[1] = ((idx // 80) % 2).astype(np.int32)
+    seg[:, seq - 100:] = -1
+    inp["positions"] = np.broadcast_to(idx.astype(np.int32), (2, seq)).copy()
+    inp["segment_ids"] = seg
+    out, lse = _run_fwd(inp)
+    _check(inp, out, lse)
+
+
 @pytest.mark.parametrize("n_tiles", [1, 3, 5])
 def test_forward_odd_tile_counts(n_tiles):
     """Sequences with an odd number of query tiles: the last pair has one tile only."""
