@@ -163,7 +163,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const uint32_t e = e_next;
-      const int u = int(e & ~kPartialBit);
+      const int u = int(e & kTileIndexMask);
       const bool partial = (e & kPartialBit) != 0;
       const int yh = qh;
       if (++li == cnt) { li = 0; ++qh; }
@@ -321,7 +321,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_co
       const uint32_t e = e_next;
       if (++li == count) li = 0;
       if (i + 1 < n_items) e_next = __ldg(list + li);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+      const int c0 = int(e & kTileIndexMask) * kTile;
       const bool partial = (e & kPartialBit) != 0;
       const int st = i & 1;                                   // Y stage, column-info buffer and barrier pair of this item
       const int* cs = s_cols + st * 4 * kTile;
@@ -538,7 +538,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       bool ok = true;
       uint32_t e_next = ldg_pinned(list);
       for (int i = 0; i < n_items && ok; ++i) {
-        const int u = int(e_next & ~kPartialBit);
+        const int u = int(e_next & kTileIndexMask);
         if (i + 1 < n_items) e_next = ldg_pinned(list + i + 1);
         const int ks = i % kDqKStages, kuse = i / kDqKStages;
         if (kuse > 0) ok = mbar_wait(&bars[Q_KEMPTY0 + ks], (kuse - 1) & 1, abort_flag, a.status, Q_KEMPTY0 + ks);
@@ -644,7 +644,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     for (int i = 0; i < n_items && ok; ++i) {
       const uint32_t e = e_next;
       if (i + 1 < n_items) e_next = ldg_pinned(list + i + 1);
-      const int c0 = int(e & ~kPartialBit) * kTile;
+      const int c0 = int(e & kTileIndexMask) * kTile;
       const bool partial = (e & kPartialBit) != 0;
       uint32_t keep[2] = {0xffffffffu, 0xffffffffu};
       if (partial) {

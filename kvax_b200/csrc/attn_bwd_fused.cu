@@ -194,7 +194,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     PH_BEGIN()
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
-      const int u = int(e_next & ~kPartialBit);
+      const int u = int(e_next & kTileIndexMask);
       const int yh = qh;
       if (++li == cnt) { li = 0; ++qh; }
       if (i + 1 < n) e_next = __ldg(list + li);
@@ -403,7 +403,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     // awaited), so that their global loads never sit in front of the exponentials
     uint32_t keep_next[2] = {0xffffffffu, 0xffffffffu};
     if (e_next & kPartialBit) {
-      const int c0 = int(e_next & ~kPartialBit) * kTile;
+      const int c0 = int(e_next & kTileIndexMask) * kTile;
       keep_next[0] = chunk_keep(c0 + cb); keep_next[1] = chunk_keep(c0 + cb + 32);
     }
     uint8_t* ds_row = smem + L::kDS + half * L::kBoxBytes + row * 128;   // this thread's 128-byte row of the dS^T tile
@@ -459,7 +459,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
 
       keep_next[0] = keep_next[1] = 0xffffffffu;
       if (i + 1 < n_items && (e_next & kPartialBit)) {
-        const int c0n = int(e_next & ~kPartialBit) * kTile;
+        const int c0n = int(e_next & kTileIndexMask) * kTile;
         keep_next[0] = chunk_keep(c0n + cb); keep_next[1] = chunk_keep(c0n + cb + 32);
       }
       PH(0)
@@ -566,7 +566,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     int li = 0, qh = first_head;
     PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
-      const int q0 = int(e_next & ~kPartialBit) * kTile + dw * 32;    // first query row this warp drains
+      const int q0 = int(e_next & kTileIndexMask) * kTile + dw * 32;    // first query row this warp drains
       const int yh = qh;
       if (++li == count) { li = 0; ++qh; }
       if (i + 1 < n_items) e_next = ldg_pinned(list + li);
