@@ -208,7 +208,8 @@ def mask_builder_numbers(q_pos, q_seg, kv_pos, kv_seg, dev, peaks, public_call_m
     for (mb, ms_) in ((2048, 4096), (64, 131072)):
         mp = (torch.arange(ms_, device=dev, dtype=torch.int32) % 1000).repeat(mb, 1)
         msg = (torch.arange(ms_, device=dev, dtype=torch.int32) // 1000).repeat(mb, 1)
-        plan = MaskPlan(mp, msg, mp, msg, spec3, True)
+        # separate query-side and kv-side arrays, so that the four inputs the byte count names are four distinct reads
+        plan = MaskPlan(mp, msg, mp.clone(), msg.clone(), spec3, True)
         plan.launch()
         t_ms = cuda_time(plan.launch, 20)
         alg = 16.0 * mb * ms_ + 48.0 * mb * ms_ / TILE
