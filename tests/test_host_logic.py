@@ -113,6 +113,25 @@ def test_context_parallel_mode_switch():
     assert kv.get_context_parallel_mode() == "auto"
 
 
+def test_context_parallel_overlap_switch_and_remote_chunk_order():
+    """The overlap switch of the all-gather schedule, and the order in which a rank finds the chunks of the other
+    ranks in a rank-major all-gather: ascending in natural order, its own two left out."""
+    import kvax_b200 as kv
+    from kvax_b200.ops.flash_attention import _chunk_of, _remote_slots
+    assert kv.get_context_parallel_overlap() is False
+    kv.set_context_parallel_overlap(True)
+    assert kv.get_context_parallel_overlap() is True
+    kv.set_context_parallel_overlap(False)
+    for cp in (2, 4, 8):
+        for permuted in (True, False):
+            for rank in range(cp):
+                slots = _remote_slots(rank, cp, permuted)
+                assert len(slots) == 2 * cp - 2 and len(set(slots)) == len(slots)
+                assert all(s // 2 != rank for s in slots)                       # none of its own
+                chunks = [_chunk_of(s // 2, s % 2, cp, permuted) for s in slots]
+                assert chunks == sorted(chunks)                                 # natural order
+
+
 def test_fp32_bridge_scales_small_output_gradients():
     """The casts around a call on fp32 tensors: an output gradient far below the fp16 range is multiplied by a power
     of two on its way in and the input gradients are divided by it on their way out, so a linear map in fp16 gives
