@@ -690,8 +690,9 @@ def main():
     if cp == 1:
         line["config"]["tile_pairs_in_reference_bounds"] = reference_visited
         # the library's default choice of forward kernel for this shape (see kvax_b200_attn_fwd_params.flags)
-        line["config"]["forward_kernel"] = ("one query tile per CTA" if S < 16384 else
-                                            ("two heads of a kv group per CTA" if (Hq // Hkv) % 2 == 0 else "two query tiles per CTA"))
+        head_pairs = (Hq // Hkv) % 2 == 0 and (S // TILE) * B * (Hq // 2) >= 2 * 148
+        line["config"]["forward_kernel"] = ("two heads of a kv group per CTA" if head_pairs or (S >= 16384 and (Hq // Hkv) % 2 == 0) else
+                                            ("two query tiles per CTA" if S >= 16384 else "one query tile per CTA"))
     if roofline:
         line["roofline"] = roofline
     if cp == 1 and mask_info:

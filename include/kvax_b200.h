@@ -224,13 +224,14 @@ typedef struct kvax_b200_attn_fwd_params {
   int32_t* status;                /* optional device int32, must be 0 on entry */
   /* 0 = everything; else bit set: 1 tile list, 2 attention kernel (see the backward). */
   int32_t stages;
-  int32_t flags;                  /* KVAX_B200_FWD_*; 0: the library picks the kernel by sequence length */
+  int32_t flags;                  /* KVAX_B200_FWD_*; 0: the library picks the kernel by shape */
 } kvax_b200_attn_fwd_params;
 
 /* Forward kernels: a CTA works on one 128-row query tile, or on two work items that share
  * every K / V tile brought on chip: two neighbouring query tiles of one head, or (grouped-query
  * attention, an even number of query heads per kv head) one query tile of two query heads of a
- * kv group.  Same results either way. */
+ * kv group.  Same results either way.  Default: head pairs when the group is even and at least two CTAs per SM
+ * remain (or from 16k kv tokens on), tile pairs for other shapes from 16k kv tokens on, else one tile. */
 enum { KVAX_B200_FWD_ONE_TILE = 1, KVAX_B200_FWD_TILE_PAIRS = 2, KVAX_B200_FWD_HEAD_PAIRS = 4,
        /* query tiles without any key tile get lse = +inf instead of the reference's 0 (flash_attention_triton.py:253-258),
           so that kvax_b200_attn_merge can tell them from rows that have keys */

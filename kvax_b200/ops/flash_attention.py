@@ -88,7 +88,8 @@ def set_forward_kernel(kernel: str) -> None:
     """Which forward kernel runs: a CTA per 128-row query tile ("one_tile"); a CTA per two work items that share
     their K / V tiles -- two neighbouring query tiles of one head ("tile_pairs") or one query tile of two query heads
     of a kv group ("head_pairs", grouped-query attention with an even group); or the library's choice ("auto",
-    default: pairs from 16k kv tokens on, head pairs when the group allows).  Same results to rounding either way."""
+    default: head pairs when the group is even and at least two CTAs per SM remain, else pairs from 16k kv tokens
+    on, else one tile).  Same results to rounding either way."""
     global _fwd_kernel
     if kernel not in _FWD_KERNELS:
         raise ValueError(f"unknown forward kernel {kernel!r}; expected one of {_FWD_KERNELS}")
