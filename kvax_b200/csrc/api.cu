@@ -251,7 +251,7 @@ BwdLayout bwd_layout(const kvax_b200_attn_bwd_params& p) {
   l.fused = use_fused(p);
   l.head_split = l.fused ? fused_head_split(s) : 1;
   l.dq = list_layout(s.batch, s.q_len, s.kv_len, 0);
-  l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total);
+  l.dkdv = list_layout(s.batch, s.kv_len, s.q_len, l.dq.total, true);
   l.sum = summary_layout(s.batch, s.q_len, s.kv_len, l.dkdv.total);
   l.delta_off = l.sum.total;
   l.acc_off = l.delta_off + align256(size_t(s.batch) * s.q_heads * s.q_len * sizeof(float));

@@ -98,11 +98,27 @@ struct FusedSmem {
   static_assert(kTotal <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
+// Mask bits of kv row r for the 64 queries [i0, i0 + 64) of a partial list entry that carries no element mask from the
+// list builder (more than kBitmapSlots partial entries in one list: rare).  Deliberately not inlined: what it needs --
+// the row's bounds, its segment id and position, the query arrays -- then lives in no register of the item loop (a
+// build of the loop that took every mask from the list builder ran 4 % faster than one that could also compute them).
+__device__ __noinline__ uint2 fused_keep_slow(const BwdArgs* a, int b, int r, int i0) {
+  const bool row_valid = r < a->tok.kv_len;
+  const RowBounds rb = load_bounds(a->mask, b, min(r, a->tok.kv_len - 1));
+  int kv_seg = KVAX_B200_PADDING_SEGMENT_ID, kv_pos = 0;
+  if (row_valid) {
+    kv_seg = __ldg(a->tok.kv_seg + (long long)b * a->tok.kv_len + r);
+    kv_pos = a->tok.sequential ? r : __ldg(a->tok.kv_pos + (long long)b * a->tok.kv_len + r);
+  }
+  return make_uint2(kv_outer_keep32(a->tok, rb, b, row_valid, kv_seg, kv_pos, i0),
+                    kv_outer_keep32(a->tok, rb, b, row_valid, kv_seg, kv_pos, i0 + 32));
+}
+
 template <int D, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                       const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
-                      const __grid_constant__ CUtensorMap tmap_dq, const BwdArgs a) {
+                      const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ BwdArgs a) {
   using L = FusedSmem<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -364,36 +380,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     const uint32_t my_t1 = tT1 + lane_base + cb;              // fp32 columns of this thread; P^T goes to the first 32 of them
     const uint32_t my_t2 = tT2 + lane_base + cb;
     const float c = a.scale_log2e;
-    const RowBounds rb = load_bounds(a.mask, b, min(r, a.tok.kv_len - 1));
-    int kv_seg = KVAX_B200_PADDING_SEGMENT_ID, kv_pos = 0;
-    if (row_valid) {
-      kv_seg = __ldg(a.tok.kv_seg + (long long)b * a.tok.kv_len + r);
-      kv_pos = a.tok.sequential ? r : __ldg(a.tok.kv_pos + (long long)b * a.tok.kv_len + r);
-    }
-    const int32_t* q_seg = a.tok.q_seg + (long long)b * q_len;
-    const int32_t* q_pos = a.tok.sequential ? nullptr : a.tok.q_pos + (long long)b * q_len;
-    const int second_from = (q_len + 1) >> 1;                 // first local query of the second half (2 r >= q_len)
-
-    // Mask bits of this kv row for the 32 queries [i0, i0 + 32).  With assume_sequential_positions the query
-    // position is its index plus the global offset of its half of the local queries, which is folded into the
-    // kv position so that the index itself can be compared.
-    auto chunk_keep = [&](int i0) -> uint32_t {
-      if (!a.tok.sequential) return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos, q_seg + i0, q_pos + i0);
-      if (i0 >= second_from || i0 + 32 <= second_from || a.tok.off_first == a.tok.off_second) {
-        const int off = (i0 >= second_from) ? a.tok.off_second : a.tok.off_first;
-        return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos - off, q_seg + i0, nullptr);
-      }
-      uint32_t bits = 0;                                      // the chunk straddles the two halves
-      if (row_valid) {
-        for (int j = 0; j < 32; ++j) {
-          const int i = i0 + j;
-          if (i < q_len) {
-            const int p = i + (i >= second_from ? a.tok.off_second : a.tok.off_first);
-            bits |= (element_allowed<true>(rb, i, __ldg(q_seg + i) == kv_seg, p >= kv_pos) ? 1u : 0u) << j;
-          }
-        }
-      }
-      return bits;
+    // Mask bits of this thread's 64 queries of partial list entry e: the element mask the list builder worked out for
+    // the first partial entries of every list (one 8-byte load), else computed by the function above.
+    const uint2* bitmap_row = reinterpret_cast<const uint2*>(a.list.bitmaps + (list_row * kBitmapSlots) * kTile + row) + half;
+    auto item_keep = [&](uint32_t e, uint32_t* k2) {
+      const uint2 w = (e & kBitmapBit) ? __ldg(bitmap_row + ((e >> kBitmapSlotShift) & (kBitmapSlots - 1)) * (kTile * 2))
+                                       : fused_keep_slow(&a, b, r, int(e & kTileIndexMask) * kTile + cb);
+      k2[0] = w.x; k2[1] = w.y;
     };
 
     bool ok = true;
@@ -402,10 +395,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     // mask bits of the coming item are worked out one item ahead (in the gap while dP^T of the current item is
     // awaited), so that their global loads never sit in front of the exponentials
     uint32_t keep_next[2] = {0xffffffffu, 0xffffffffu};
-    if (e_next & kPartialBit) {
-      const int c0 = int(e_next & kTileIndexMask) * kTile;
-      keep_next[0] = chunk_keep(c0 + cb); keep_next[1] = chunk_keep(c0 + cb + 32);
-    }
+    if (e_next & kPartialBit) item_keep(e_next, keep_next);
     uint8_t* ds_row = smem + L::kDS + half * L::kBoxBytes + row * 128;   // this thread's 128-byte row of the dS^T tile
     PH_BEGIN()
     for (int i = 0; i < n_items && ok; ++i) {
@@ -458,10 +448,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
       PH(3)
 
       keep_next[0] = keep_next[1] = 0xffffffffu;
-      if (i + 1 < n_items && (e_next & kPartialBit)) {
-        const int c0n = int(e_next & kTileIndexMask) * kTile;
-        keep_next[0] = chunk_keep(c0n + cb); keep_next[1] = chunk_keep(c0n + cb + 32);
-      }
+      if (i + 1 < n_items && (e_next & kPartialBit)) item_keep(e_next, keep_next);
       PH(0)
 
       // ---- B: dS^T = P^T * (dP^T - delta) -> bf16 -> the dS^T tile in shared memory

@@ -142,6 +142,35 @@ __device__ __forceinline__ uint32_t keep_bits32(const RowBounds& rb, int i0, int
   return bits;
 }
 
+// Mask bits of one kv row (kv-outer orientation) for the 32 queries [i0, i0 + 32) of batch row b.  `kv_pos` is the
+// row's position, i.e. its index under assume_sequential_positions; the query position is then the query's index plus
+// the global offset of its half of the local queries, which is folded into the kv position so that the index itself
+// can be compared.  Used by the list builder (element masks of marked entries) and by the backward kernels on
+// entries without one: same function, same bits.
+__device__ __forceinline__ uint32_t kv_outer_keep32(const TokenInfo& tok, const RowBounds& rb, int b, bool row_valid,
+                                                    int kv_seg, int kv_pos, int i0) {
+  const int q_len = tok.q_len;
+  const int32_t* q_seg = tok.q_seg + (long long)b * q_len;
+  if (!tok.sequential)
+    return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos, q_seg + i0, tok.q_pos + (long long)b * q_len + i0);
+  const int second_from = (q_len + 1) >> 1;                 // first local query of the second half (2 r >= q_len)
+  if (i0 >= second_from || i0 + 32 <= second_from || tok.off_first == tok.off_second) {
+    const int off = (i0 >= second_from) ? tok.off_second : tok.off_first;
+    return keep_bits32<true>(rb, i0, q_len, row_valid, kv_seg, kv_pos - off, q_seg + i0, nullptr);
+  }
+  uint32_t bits = 0;                                        // the chunk straddles the two halves
+  if (row_valid) {
+    for (int j = 0; j < 32; ++j) {
+      const int i = i0 + j;
+      if (i < q_len) {
+        const int p = i + (i >= second_from ? tok.off_second : tok.off_first);
+        bits |= (element_allowed<true>(rb, i, __ldg(q_seg + i) == kv_seg, p >= kv_pos) ? 1u : 0u) << j;
+      }
+    }
+  }
+  return bits;
+}
+
 // ---------------------------------------------------------------------------
 // Tile lists (built by schedule.cu): for every (batch, outer tile) the inner tiles to
 // visit, ascending; bit 31 marks tiles that need the element-level mask.

@@ -184,10 +184,7 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
       __syncthreads();
       // C: ordered compaction by warp 0.  The first kBitmapSlots partial entries of a list get an element
       // mask of their own (step D) and are marked.
-      // (the callers ask for them on the forward lists only: the fused backward works its mask bits out one item ahead,
-      // in a gap of its pipeline, and gained nothing measurable from them; kv-outer lists with
-      // assume_sequential_positions could not have them, the consumer folds per-half query offsets in itself)
-      const bool with_bitmaps = a.bitmaps != nullptr && !(kKvOuter && a.tok.sequential);
+      const bool with_bitmaps = a.bitmaps != nullptr;
       const int partial_before = s_partial;
       if (t < 32) {
         int cnt = s_count, pcnt = partial_before;
@@ -212,16 +209,16 @@ __global__ void __launch_bounds__(kTile) schedule_kernel(const ScheduleArgs a) {
       // would call on the same arguments
       if (with_bitmaps) {
         const int slot_end = min(s_partial, kBitmapSlots);
-        const int32_t* inner_seg = kKvOuter ? a.tok.q_seg + (long long)b * a.tok.q_len : a.tok.kv_seg + (long long)b * a.tok.kv_len;
-        const int32_t* inner_pos = kKvOuter ? a.tok.q_pos + (long long)b * a.tok.q_len
-                                            : (a.tok.sequential ? nullptr : a.tok.kv_pos + (long long)b * a.tok.kv_len);
+        const int32_t* inner_seg = a.tok.kv_seg + (long long)b * a.tok.kv_len;
+        const int32_t* inner_pos = a.tok.sequential ? nullptr : a.tok.kv_pos + (long long)b * a.tok.kv_len;
         for (int slot = partial_before; slot < slot_end; ++slot) {
           const int c0 = s_slot_tile[slot] * kTile;
           uint32_t w[4];
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch)
-            w[ch] = keep_bits32<kKvOuter>(rb, c0 + ch * 32, a.inner_len, row_valid, o_seg, o_pos, inner_seg + c0 + ch * 32,
-                                          inner_pos ? inner_pos + c0 + ch * 32 : nullptr);
+            w[ch] = kKvOuter ? kv_outer_keep32(a.tok, rb, b, row_valid, o_seg, o_pos, c0 + ch * 32)
+                             : keep_bits32<false>(rb, c0 + ch * 32, a.inner_len, row_valid, o_seg, o_pos, inner_seg + c0 + ch * 32,
+                                                  inner_pos ? inner_pos + c0 + ch * 32 : nullptr);
           a.bitmaps[(((long long)b * a.n_outer_tiles + ot) * kBitmapSlots + slot) * kTile + t] = make_uint4(w[0], w[1], w[2], w[3]);
         }
         __syncthreads();                        // s_slot_tile is reused by the next pass

@@ -83,6 +83,27 @@ def test_fused_backward_sequential_and_global_positions(sequential):
     _check(inp, dq, dk, dv)
 
 
+@pytest.mark.parametrize("sequential", [False, True])
+@pytest.mark.parametrize("mode", ["fused", "two_kernel"])
+def test_backward_many_partial_tiles(mode, sequential):
+    """Segments interleaved in runs of 48 tokens with global positions: every visited tile pair is a partial one, up to
+    17 per list.  The first eight entries of a kv-outer list take the element masks the list builder worked out, the
+    others are masked inside the kernels (the fused backward's fallback): both against the oracle, with position
+    arrays and with assume_sequential_positions."""
+    seq = 2048 + 70
+    cfg = gen.small_config(seq=seq, batch=2, hq=4, hkv=1, head_dim=128)
+    inp = dict(gen.make_inputs(cfg, seed=47))
+    idx = np.arange(seq)
+    seg = np.broadcast_to(((idx // 48) % 3).astype(np.int32), (2, seq)).copy()
+    seg[1] = ((idx // 80) % 2).astype(np.int32)
+    seg[:, seq - 100:] = -1
+    inp["positions"] = np.broadcast_to(idx.astype(np.int32), (2, seq)).copy()
+    inp["segment_ids"] = seg
+    inp = _zero_pad_dout(inp)
+    _, dq, dk, dv = _run_fwd_bwd(inp, sequential=sequential, mode=mode)
+    _check(inp, dq, dk, dv)
+
+
 @pytest.mark.parametrize("bwd_blocks", [(64, 128), (64, 64), (128, 64)])
 def test_backward_mask_block_sizes(bwd_blocks):
     cfg = gen.small_config(seq=1024, hq=2, hkv=1, head_dim=128, doc_min=40, doc_max=500)
