@@ -392,7 +392,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     bool ok = true;
     uint32_t e_next = ldg_pinned(list);
     int li = 0;
-    // mask bits of the coming item are worked out one item ahead (in the gap while dP^T of the current item is
+    // mask bits of the coming item are fetched one item ahead (in the gap while dP^T of the current item is
     // awaited), so that their global loads never sit in front of the exponentials
     uint32_t keep_next[2] = {0xffffffffu, 0xffffffffu};
     if (e_next & kPartialBit) item_keep(e_next, keep_next);
